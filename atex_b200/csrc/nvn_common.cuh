@@ -1,0 +1,228 @@
+// Device-side building blocks shared by all nvnorms kernels: typed packs for
+// vector loads/stores, dtype conversion, and the deterministic reductions
+// (warp shuffle butterfly -> shared-memory combine -> cluster DSMEM combine).
+//
+// Replaces the helper layer of the reference (atex/nv_norms/cc/kernels/norm_util.h:
+// Pack/Load/Store :29-180, WelfordWarpReduce/BlockAllReduce :423-464) with
+// sm_100a-only code: 128-bit accesses, explicit shuffles, thread-block clusters.
+#pragma once
+
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nvn {
+
+namespace cg = cooperative_groups;
+
+// ---------------------------------------------------------------------------
+// dtype conversion (compute type is always fp32)
+// ---------------------------------------------------------------------------
+template <typename T>
+struct Cvt;
+template <>
+struct Cvt<float> {
+  static __device__ __forceinline__ float to_f32(float v) { return v; }
+  static __device__ __forceinline__ float from_f32(float v) { return v; }
+};
+template <>
+struct Cvt<__half> {
+  static __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
+};
+template <>
+struct Cvt<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) {
+    return __float2bfloat16_rn(v);
+  }
+};
+
+// Elements of T in one 128-bit access.
+template <typename T>
+struct VecTraits {
+  static constexpr int kFull = 16 / sizeof(T);
+};
+
+// EPV elements of T moved as one access of EPV*sizeof(T) bytes (16, 8, 4 or 2).
+template <typename T, int EPV>
+struct alignas(sizeof(T) * EPV) Pack {
+  T v[EPV];
+};
+
+// Streaming (read-once / write-once) global accesses.  Activations are touched
+// exactly once per kernel, so they are marked evict-first; parameters and
+// statistics use ordinary cached loads.
+template <typename T, int EPV>
+__device__ __forceinline__ Pack<T, EPV> load_stream(const T* base, int64_t elem_off) {
+  using P = Pack<T, EPV>;
+  const P* p = reinterpret_cast<const P*>(base + elem_off);
+  if constexpr (sizeof(P) == 16) {
+    union {
+      uint4 u;
+      P p;
+    } c;
+    c.u = __ldcs(reinterpret_cast<const uint4*>(p));
+    return c.p;
+  } else if constexpr (sizeof(P) == 8) {
+    union {
+      uint2 u;
+      P p;
+    } c;
+    c.u = __ldcs(reinterpret_cast<const uint2*>(p));
+    return c.p;
+  } else if constexpr (sizeof(P) == 4) {
+    union {
+      unsigned u;
+      P p;
+    } c;
+    c.u = __ldcs(reinterpret_cast<const unsigned*>(p));
+    return c.p;
+  } else {
+    return *p;
+  }
+}
+
+template <typename T, int EPV>
+__device__ __forceinline__ void store_stream(T* base, int64_t elem_off, const Pack<T, EPV>& v) {
+  using P = Pack<T, EPV>;
+  P* p = reinterpret_cast<P*>(base + elem_off);
+  if constexpr (sizeof(P) == 16) {
+    union {
+      uint4 u;
+      P p;
+    } c;
+    c.p = v;
+    __stcs(reinterpret_cast<uint4*>(p), c.u);
+  } else if constexpr (sizeof(P) == 8) {
+    union {
+      uint2 u;
+      P p;
+    } c;
+    c.p = v;
+    __stcs(reinterpret_cast<uint2*>(p), c.u);
+  } else if constexpr (sizeof(P) == 4) {
+    union {
+      unsigned u;
+      P p;
+    } c;
+    c.p = v;
+    __stcs(reinterpret_cast<unsigned*>(p), c.u);
+  } else {
+    *p = v;
+  }
+}
+
+// EPV consecutive fp32 parameters (gamma / beta / dgamma ...).  When EPV > 1
+// the dispatcher guarantees 16-byte alignment of the base pointer.
+template <int EPV>
+__device__ __forceinline__ void load_params(const float* __restrict__ p, int64_t off,
+                                            float (&out)[EPV]) {
+  if constexpr (EPV % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < EPV / 4; ++i) {
+      float4 t = __ldg(reinterpret_cast<const float4*>(p + off) + i);
+      out[4 * i + 0] = t.x;
+      out[4 * i + 1] = t.y;
+      out[4 * i + 2] = t.z;
+      out[4 * i + 3] = t.w;
+    }
+  } else if constexpr (EPV == 2) {
+    float2 t = __ldg(reinterpret_cast<const float2*>(p + off));
+    out[0] = t.x;
+    out[1] = t.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < EPV; ++i) out[i] = __ldg(p + off + i);
+  }
+}
+
+template <int EPV>
+__device__ __forceinline__ void store_params(float* __restrict__ p, int64_t off,
+                                             const float (&v)[EPV]) {
+  if constexpr (EPV % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < EPV / 4; ++i) {
+      reinterpret_cast<float4*>(p + off)[i] =
+          make_float4(v[4 * i + 0], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    }
+  } else if constexpr (EPV == 2) {
+    *reinterpret_cast<float2*>(p + off) = make_float2(v[0], v[1]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < EPV; ++i) p[off + i] = v[i];
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Row-group all-reduce (sum) of NV values.
+//
+// A "row group" is TPR consecutive threads of a CTA (TPR a power of two).  For
+// TPR <= 32 the sum is a shuffle butterfly.  For TPR > 32 each warp's butterfly
+// result goes to shared memory and every thread adds the TPR/32 warp values in
+// index order.  With CS > 1 the CTA total is published in shared memory and
+// every CTA of the thread-block cluster adds the CS totals in rank order through
+// distributed shared memory.  The order of every addition is fixed, so the
+// result is identical in all threads and from run to run.
+//
+// Shared-memory slots are double-buffered on `phase` (toggled by the caller
+// after each call) so one barrier per reduction is enough.
+// ---------------------------------------------------------------------------
+template <int NV, int BLOCK>
+struct ReduceSmem {
+  float warp_part[2][NV][BLOCK / 32];
+  float cta_total[2][NV];
+};
+
+template <int NV, int TPR, int BLOCK, int CS>
+__device__ __forceinline__ void group_allreduce(float (&v)[NV], ReduceSmem<NV, BLOCK>& sm,
+                                                int& phase) {
+  constexpr int kShuffleSpan = TPR < 32 ? TPR : 32;
+#pragma unroll
+  for (int off = kShuffleSpan / 2; off > 0; off >>= 1) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) v[k] += __shfl_xor_sync(0xffffffffu, v[k], off);
+  }
+  if constexpr (TPR > 32) {
+    constexpr int WPR = TPR / 32;  // warps per row group
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    if (lane == 0) {
+#pragma unroll
+      for (int k = 0; k < NV; ++k) sm.warp_part[phase][k][warp] = v[k];
+    }
+    __syncthreads();
+    const int first = (warp / WPR) * WPR;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < WPR; ++w) s += sm.warp_part[phase][k][first + w];
+      v[k] = s;
+    }
+  }
+  if constexpr (CS > 1) {
+    static_assert(TPR == BLOCK, "a cluster shares one row, so the CTA is one row group");
+    cg::cluster_group cluster = cg::this_cluster();
+    if (threadIdx.x == 0) {
+#pragma unroll
+      for (int k = 0; k < NV; ++k) sm.cta_total[phase][k] = v[k];
+    }
+    cluster.sync();
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      float s = 0.f;
+#pragma unroll
+      for (int r = 0; r < CS; ++r) {
+        const float* remote = cluster.map_shared_rank(&sm.cta_total[phase][k], r);
+        s += *remote;
+      }
+      v[k] = s;
+    }
+  }
+  phase ^= 1;
+}
+
+}  // namespace nvn

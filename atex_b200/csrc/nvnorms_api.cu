@@ -1,0 +1,538 @@
+// C ABI of libnvnorms (include/nvnorms.h): argument checking, the dispatch
+// table that maps a problem (dtype, N, C, D, layout, alignment) to a kernel
+// variant, workspace carving and the launches.
+//
+// Takes the place of the host halves of the reference functors
+// (atex/nv_norms/cc/kernels/fused_layer_norm_op.cu:805-1030,
+//  atex/nv_norms/cc/kernels/fused_instance_norm_op.cu:820-906, 1203-1561) and of
+// the shape bookkeeping in the OpKernels (fused_layer_norm_op.cc:252-282,
+// fused_instance_norm_op.cc:25-34, 333-376).
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <atomic>
+#include <mutex>
+#include <vector>
+
+#include "../../include/nvnorms.h"
+#include "nvn_host.h"
+#include "twophase.h"
+
+namespace nvn {
+
+namespace {
+std::atomic<uint64_t> g_launches{0};
+thread_local int t_last_cuda_error = 0;
+std::atomic<int> g_sm_count{0};
+
+struct Shape {
+  int tpr, vpt, cs;
+};
+#define X(I, TPR, VPT, CS) {TPR, VPT, CS},
+const Shape kFwdShapes[] = {NVN_ROW_SHAPES_FWD(X)};
+const Shape kBwdShapes[] = {NVN_ROW_SHAPES_BWD(X)};
+const Shape kScalarShapes[] = {NVN_ROW_SHAPES_SCALAR(X)};
+#undef X
+constexpr int kNumFwd = sizeof(kFwdShapes) / sizeof(Shape);
+constexpr int kNumBwd = sizeof(kBwdShapes) / sizeof(Shape);
+constexpr int kNumScalar = sizeof(kScalarShapes) / sizeof(Shape);
+
+inline int64_t cap(const Shape& s) { return static_cast<int64_t>(s.tpr) * s.vpt * s.cs; }
+
+// Smallest capacity that holds `nvec` vectors; among equals the first listed.
+// NVN_FORCE_FWD_SHAPE / NVN_FORCE_BWD_SHAPE (a table index) override the
+// choice when that shape is large enough: used for tuning runs only.
+int pick_shape(const Shape* table, int n, int64_t nvec, const char* force_env) {
+  if (force_env != nullptr) {
+    const char* v = getenv(force_env);
+    if (v != nullptr && *v != '\0') {
+      const int idx = atoi(v);
+      if (idx >= 0 && idx < n && cap(table[idx]) >= nvec) return idx;
+    }
+  }
+  int best = -1;
+  for (int i = 0; i < n; ++i) {
+    if (cap(table[i]) < nvec) continue;
+    if (best < 0 || cap(table[i]) < cap(table[best])) best = i;
+  }
+  return best;
+}
+
+inline bool aligned(const void* p, size_t a) {
+  return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
+}
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+inline size_t dtype_size(int dtype) { return dtype == NVN_F32 ? 4 : 2; }
+inline int full_epv(int dtype) { return dtype == NVN_F32 ? 4 : 8; }
+
+typedef cudaError_t (*RowsFn)(bool, bool, int, const RowsArgs&, cudaStream_t, bool, RowsPlan*);
+RowsFn rows_fn(int dtype, bool bwd) {
+  switch (dtype) {
+    case NVN_F32:
+      return bwd ? rows_f32_bwd : rows_f32_fwd;
+    case NVN_F16:
+      return bwd ? rows_f16_bwd : rows_f16_fwd;
+    default:
+      return bwd ? rows_bf16_bwd : rows_bf16_fwd;
+  }
+}
+
+int fail_cuda(cudaError_t e) {
+  t_last_cuda_error = static_cast<int>(e);
+  (void)cudaGetLastError();
+  return NVN_ERR_CUDA;
+}
+
+// ---------------------------------------------------------------------------
+// Plan for a contiguous-row problem ([rows, D], LayerNorm or "NC..." InstanceNorm)
+// ---------------------------------------------------------------------------
+struct RowProblemPlan {
+  bool two_phase;
+  bool scalar;
+  int shape;       // row-cached variant
+  RowsPlan rows;   // filled by a dry run
+  R2Plan r2;       // two-phase variant
+  // workspace carving (byte offsets)
+  size_t off_part, off_coef, off_colpart, bytes;
+  int64_t colpart_rows;  // P of the column reduction (LayerNorm backward / IN backward)
+};
+
+// vec_ok: every pointer is 16-byte aligned (assumed true for size queries).
+int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int64_t N,
+              int64_t C, bool vec_ok, RowProblemPlan* p) {
+  memset(p, 0, sizeof(*p));
+  const int V = full_epv(dtype);
+  p->scalar = !(vec_ok && D % V == 0);
+  const int epv = p->scalar ? 1 : V;
+  const int64_t nvec = D / epv;
+  const Shape* table = p->scalar ? kScalarShapes : (bwd ? kBwdShapes : kFwdShapes);
+  const int ntab = p->scalar ? kNumScalar : (bwd ? kNumBwd : kNumFwd);
+  const char* env = p->scalar ? nullptr : (bwd ? "NVN_FORCE_BWD_SHAPE" : "NVN_FORCE_FWD_SHAPE");
+  p->shape = pick_shape(table, ntab, nvec, env);
+  p->two_phase = p->shape < 0;
+  size_t off = 0;
+  if (!p->two_phase) {
+    RowsArgs a = {};
+    a.N = rows;
+    a.D = D;
+    a.C = C;
+    cudaError_t e = rows_fn(dtype, bwd)(row_affine, p->scalar, p->shape, a, nullptr, true,
+                                        &p->rows);
+    if (e != cudaSuccess) return fail_cuda(e);
+    if (bwd) {
+      p->colpart_rows = row_affine ? N : p->rows.partial_rows;
+      p->off_colpart = off;
+      off += align_up(static_cast<size_t>(p->colpart_rows) * 2 * (row_affine ? C : D) * 4, 256);
+    }
+  } else {
+    if (rows > 0x7fffffffLL) return NVN_ERR_UNSUPPORTED;
+    p->r2 = r2_plan(rows, D, epv, bwd && !row_affine);
+    p->off_part = off;
+    off += align_up(static_cast<size_t>(rows) * p->r2.nchunks * (bwd ? 2 : 3) * 4, 256);
+    if (bwd) {
+      p->off_coef = off;
+      off += align_up(static_cast<size_t>(rows) * 2 * 4, 256);
+      p->colpart_rows = row_affine ? N : p->r2.slices;
+      p->off_colpart = off;
+      off += align_up(static_cast<size_t>(p->colpart_rows) * 2 * (row_affine ? C : D) * 4, 256);
+    }
+  }
+  p->bytes = off;
+  return NVN_OK;
+}
+
+size_t rows_workspace_bytes(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D,
+                            int64_t N, int64_t C) {
+  if (rows <= 0 || D <= 0) return 0;
+  RowProblemPlan pv, ps;
+  size_t b = 0;
+  if (plan_rows(dtype, bwd, row_affine, rows, D, N, C, true, &pv) == NVN_OK) b = pv.bytes;
+  if (plan_rows(dtype, bwd, row_affine, rows, D, N, C, false, &ps) == NVN_OK)
+    b = std::max(b, ps.bytes);
+  return b;
+}
+
+int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x,
+             const float* gamma, const float* beta, const float* mean_in, const float* ivar_in,
+             int64_t rows, int64_t D, int64_t N, int64_t C, float eps, void* out, float* mean,
+             float* ivar, float* dgamma, float* dbeta, void* ws, size_t ws_bytes,
+             cudaStream_t stream) {
+  bool vec_ok = aligned(x, 16) && aligned(out, 16) && aligned(gamma, 16);
+  if (bwd) {
+    vec_ok = vec_ok && aligned(dy, 16);
+  } else {
+    vec_ok = vec_ok && aligned(beta, 16);
+  }
+  RowProblemPlan p;
+  int st = plan_rows(dtype, bwd, row_affine, rows, D, N, C, vec_ok, &p);
+  if (st != NVN_OK) return st;
+  if (p.bytes > 0 && (ws == nullptr || !aligned(ws, 256) || ws_bytes < p.bytes))
+    return NVN_ERR_WORKSPACE;
+  char* wsb = static_cast<char*>(ws);
+  const int64_t F = row_affine ? C : D;
+
+  if (!p.two_phase) {
+    RowsArgs a = {};
+    a.x = x;
+    a.dy = dy;
+    a.gamma = gamma;
+    a.beta = beta;
+    a.mean_in = mean_in;
+    a.ivar_in = ivar_in;
+    a.out = out;
+    a.mean = mean;
+    a.ivar = ivar;
+    a.ws = bwd ? reinterpret_cast<float*>(wsb + p.off_colpart) : nullptr;
+    a.N = rows;
+    a.D = D;
+    a.C = C;
+    a.eps = eps;
+    RowsPlan rp;
+    cudaError_t e =
+        rows_fn(dtype, bwd)(row_affine, p.scalar, p.shape, a, stream, false, &rp);
+    if (e != cudaSuccess) return fail_cuda(e);
+  } else {
+    R2Args a = {};
+    a.x = x;
+    a.dy = dy;
+    a.gamma = gamma;
+    a.beta = beta;
+    a.mean = bwd ? const_cast<float*>(mean_in) : mean;
+    a.ivar = bwd ? const_cast<float*>(ivar_in) : ivar;
+    a.out = out;
+    a.ws_part = reinterpret_cast<float*>(wsb + p.off_part);
+    a.ws_coef = bwd ? reinterpret_cast<float*>(wsb + p.off_coef) : nullptr;
+    a.ws_colpart = bwd ? reinterpret_cast<float*>(wsb + p.off_colpart) : nullptr;
+    a.rows = rows;
+    a.D = D;
+    a.C = C;
+    a.eps = eps;
+    a.row_affine = row_affine;
+    cudaError_t e = r2_launch(dtype, bwd, p.scalar, a, p.r2, stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+  }
+  if (bwd) {
+    cudaError_t e = colreduce_launch(reinterpret_cast<const float*>(wsb + p.off_colpart),
+                                     p.colpart_rows, F, dgamma, dbeta, stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+  }
+  return NVN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Plan for channels-last InstanceNorm (x[n, d, c])
+// ---------------------------------------------------------------------------
+struct NlcPlan {
+  bool scalar;
+  S2Plan s2;
+  size_t off_part, off_coef, off_colpart, bytes;
+};
+
+int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, NlcPlan* p) {
+  memset(p, 0, sizeof(*p));
+  const int V = full_epv(dtype);
+  p->scalar = !(vec_ok && C % V == 0);
+  const int epv = p->scalar ? 1 : V;
+  if (N > 65535) return NVN_ERR_UNSUPPORTED;
+  p->s2 = s2_plan(N, C, D, epv);
+  if (p->s2.ctiles > 65535) return NVN_ERR_UNSUPPORTED;
+  size_t off = 0;
+  p->off_part = off;
+  off += align_up(static_cast<size_t>(N) * p->s2.nchunks * (bwd ? 2 : 3) * C * 4, 256);
+  if (bwd) {
+    p->off_coef = off;
+    off += align_up(static_cast<size_t>(N) * 3 * C * 4, 256);
+    p->off_colpart = off;
+    off += align_up(static_cast<size_t>(N) * 2 * C * 4, 256);
+  }
+  p->bytes = off;
+  return NVN_OK;
+}
+
+int run_nlc(int dtype, bool bwd, const void* dy, const void* x, const float* gamma,
+            const float* beta, const float* mean_in, const float* ivar_in, int64_t N, int64_t C,
+            int64_t D, float eps, void* out, float* mean, float* ivar, float* dgamma,
+            float* dbeta, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  bool vec_ok = aligned(x, 16) && aligned(out, 16) && (!bwd || aligned(dy, 16));
+  NlcPlan p;
+  int st = plan_nlc(dtype, bwd, N, C, D, vec_ok, &p);
+  if (st != NVN_OK) return st;
+  if (ws == nullptr || !aligned(ws, 256) || ws_bytes < p.bytes) return NVN_ERR_WORKSPACE;
+  char* wsb = static_cast<char*>(ws);
+  S2Args a = {};
+  a.x = x;
+  a.dy = dy;
+  a.gamma = gamma;
+  a.beta = beta;
+  a.mean = bwd ? const_cast<float*>(mean_in) : mean;
+  a.ivar = bwd ? const_cast<float*>(ivar_in) : ivar;
+  a.out = out;
+  a.ws_part = reinterpret_cast<float*>(wsb + p.off_part);
+  a.ws_coef = bwd ? reinterpret_cast<float*>(wsb + p.off_coef) : nullptr;
+  a.ws_colpart = bwd ? reinterpret_cast<float*>(wsb + p.off_colpart) : nullptr;
+  a.N = N;
+  a.C = C;
+  a.D = D;
+  a.eps = eps;
+  cudaError_t e = s2_launch(dtype, bwd, p.scalar, a, p.s2, stream);
+  if (e != cudaSuccess) return fail_cuda(e);
+  if (bwd) {
+    e = colreduce_launch(a.ws_colpart, N, C, dgamma, dbeta, stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+  }
+  return NVN_OK;
+}
+
+int zero_grads(float* dgamma, float* dbeta, int64_t F, cudaStream_t stream) {
+  if (F <= 0) return NVN_OK;
+  cudaError_t e = cudaMemsetAsync(dgamma, 0, static_cast<size_t>(F) * 4, stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(dbeta, 0, static_cast<size_t>(F) * 4, stream);
+  return e == cudaSuccess ? NVN_OK : fail_cuda(e);
+}
+
+inline bool valid_dtype(int d) { return d == NVN_F32 || d == NVN_F16 || d == NVN_BF16; }
+
+}  // namespace
+
+int device_sm_count() {
+  int v = g_sm_count.load(std::memory_order_relaxed);
+  if (v > 0) return v;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+    (void)cudaGetLastError();
+    return 148;  // B200; only reached when no device is usable
+  }
+  g_sm_count.store(v, std::memory_order_relaxed);
+  return v;
+}
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+}  // namespace nvn
+
+using namespace nvn;
+
+extern "C" {
+
+int nvn_version(void) { return 100; }
+
+const char* nvn_status_string(int status) {
+  switch (status) {
+    case NVN_OK:
+      return "ok";
+    case NVN_ERR_INVALID_ARGUMENT:
+      return "invalid argument";
+    case NVN_ERR_AXIS_RANGE:
+      return "axis contains invalid value";
+    case NVN_ERR_AXIS_NOT_PACKED:
+      return "axis is not packed from last dim.";
+    case NVN_ERR_DATA_FORMAT:
+      return "We only accept 'NC...' or 'N...C' data format";
+    case NVN_ERR_RANK:
+      return "input rank too small";
+    case NVN_ERR_WORKSPACE:
+      return "workspace missing, misaligned or too small";
+    case NVN_ERR_CUDA:
+      return "CUDA runtime error";
+    case NVN_ERR_UNSUPPORTED:
+      return "problem size not supported";
+    case NVN_ERR_LIMIT:
+      return "problem size exceeds a built-in capacity";
+    default:
+      return "unknown status";
+  }
+}
+
+int nvn_last_cuda_error(void) { return t_last_cuda_error; }
+
+uint64_t nvn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int nvn_ln_dims(int rank, const int64_t* dims, int n_axis, const int* axis, int64_t* N,
+                int64_t* D) {
+  if (dims == nullptr || N == nullptr || D == nullptr || n_axis < 0 ||
+      (n_axis > 0 && axis == nullptr))
+    return NVN_ERR_INVALID_ARGUMENT;
+  if (rank < 1) return NVN_ERR_RANK;
+  if (n_axis == 0) return NVN_ERR_AXIS_NOT_PACKED;
+  std::vector<int> ax;
+  ax.reserve(n_axis);
+  for (int i = 0; i < n_axis; ++i) {
+    const int a = axis[i] < 0 ? rank + axis[i] : axis[i];
+    if (a < 0 || a >= rank) return NVN_ERR_AXIS_RANGE;
+    ax.push_back(a);
+  }
+  std::sort(ax.begin(), ax.end());
+  ax.erase(std::unique(ax.begin(), ax.end()), ax.end());
+  if (ax[0] != rank - static_cast<int>(ax.size())) return NVN_ERR_AXIS_NOT_PACKED;
+  int64_t n = 1, d = 1;
+  for (int i = 0; i < rank; ++i) {
+    if (dims[i] < 0) return NVN_ERR_INVALID_ARGUMENT;
+    if (i >= ax[0]) {
+      d *= dims[i];
+    } else {
+      n *= dims[i];
+    }
+  }
+  *N = n;
+  *D = d;
+  return NVN_OK;
+}
+
+int nvn_in_dims(int rank, const int64_t* dims, const char* data_format, int64_t* N, int64_t* C,
+                int64_t* D, int* channel_first) {
+  if (dims == nullptr || data_format == nullptr || N == nullptr || C == nullptr ||
+      D == nullptr || channel_first == nullptr)
+    return NVN_ERR_INVALID_ARGUMENT;
+  const size_t len = strlen(data_format);
+  if (!(len > 2 && data_format[0] == 'N' &&
+        (data_format[1] == 'C' || data_format[len - 1] == 'C')))
+    return NVN_ERR_DATA_FORMAT;
+  if (rank < 4) return NVN_ERR_RANK;
+  const bool cf = data_format[1] == 'C';
+  for (int i = 0; i < rank; ++i)
+    if (dims[i] < 0) return NVN_ERR_INVALID_ARGUMENT;
+  *N = dims[0];
+  *C = cf ? dims[1] : dims[rank - 1];
+  int64_t d = 1;
+  const int lo = cf ? 2 : 1, hi = cf ? rank : rank - 1;
+  for (int i = lo; i < hi; ++i) d *= dims[i];
+  *D = d;
+  *channel_first = cf ? 1 : 0;
+  return NVN_OK;
+}
+
+size_t nvn_ln_fwd_workspace_bytes(int dtype, int64_t N, int64_t D) {
+  if (!valid_dtype(dtype)) return 0;
+  return rows_workspace_bytes(dtype, false, false, N, D, N, 1);
+}
+
+size_t nvn_ln_bwd_workspace_bytes(int dtype, int64_t N, int64_t D) {
+  if (!valid_dtype(dtype)) return 0;
+  return rows_workspace_bytes(dtype, true, false, N, D, N, 1);
+}
+
+static size_t in_workspace_bytes(int dtype, bool bwd, int64_t N, int64_t C, int64_t D,
+                                 int channel_first) {
+  if (!valid_dtype(dtype) || N <= 0 || C <= 0 || D <= 0) return 0;
+  if (channel_first || C == 1)
+    return rows_workspace_bytes(dtype, bwd, true, N * C, D, N, C);
+  NlcPlan pv, ps;
+  size_t b = 0;
+  if (plan_nlc(dtype, bwd, N, C, D, true, &pv) == NVN_OK) b = pv.bytes;
+  if (plan_nlc(dtype, bwd, N, C, D, false, &ps) == NVN_OK) b = std::max(b, ps.bytes);
+  return b;
+}
+
+size_t nvn_in_fwd_workspace_bytes(int dtype, int64_t N, int64_t C, int64_t D,
+                                  int channel_first) {
+  return in_workspace_bytes(dtype, false, N, C, D, channel_first);
+}
+
+size_t nvn_in_bwd_workspace_bytes(int dtype, int64_t N, int64_t C, int64_t D,
+                                  int channel_first) {
+  return in_workspace_bytes(dtype, true, N, C, D, channel_first);
+}
+
+int nvn_ln_fwd(int dtype, const void* x, const float* gamma, const float* beta, int64_t N,
+               int64_t D, float epsilon, void* y, float* mean, float* inv_std, void* workspace,
+               size_t workspace_bytes, void* stream) {
+  if (!valid_dtype(dtype) || N < 0 || D < 0) return NVN_ERR_INVALID_ARGUMENT;
+  if (N == 0 || D == 0) return NVN_OK;
+  if (x == nullptr || gamma == nullptr || beta == nullptr || y == nullptr || mean == nullptr ||
+      inv_std == nullptr)
+    return NVN_ERR_INVALID_ARGUMENT;
+  return run_rows(dtype, false, false, nullptr, x, gamma, beta, nullptr, nullptr, N, D, N, 1,
+                  epsilon, y, mean, inv_std, nullptr, nullptr, workspace, workspace_bytes,
+                  static_cast<cudaStream_t>(stream));
+}
+
+int nvn_ln_bwd(int dtype, const void* dy, const void* x, const float* gamma, const float* mean,
+               const float* inv_std, int64_t N, int64_t D, void* dx, float* dgamma,
+               float* dbeta, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!valid_dtype(dtype) || N < 0 || D < 0) return NVN_ERR_INVALID_ARGUMENT;
+  if (D > 0 && (dgamma == nullptr || dbeta == nullptr)) return NVN_ERR_INVALID_ARGUMENT;
+  if (N == 0 || D == 0) return zero_grads(dgamma, dbeta, D, static_cast<cudaStream_t>(stream));
+  if (dy == nullptr || x == nullptr || gamma == nullptr || mean == nullptr ||
+      inv_std == nullptr || dx == nullptr)
+    return NVN_ERR_INVALID_ARGUMENT;
+  return run_rows(dtype, true, false, dy, x, gamma, nullptr, mean, inv_std, N, D, N, 1, 0.f, dx,
+                  nullptr, nullptr, dgamma, dbeta, workspace, workspace_bytes,
+                  static_cast<cudaStream_t>(stream));
+}
+
+int nvn_in_fwd(int dtype, const void* x, const float* gamma, const float* beta, int64_t N,
+               int64_t C, int64_t D, int channel_first, float epsilon, void* y, float* mean,
+               float* inv_std, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!valid_dtype(dtype) || N < 0 || C < 0 || D < 0) return NVN_ERR_INVALID_ARGUMENT;
+  if (N == 0 || C == 0 || D == 0) return NVN_OK;
+  if (x == nullptr || gamma == nullptr || beta == nullptr || y == nullptr || mean == nullptr ||
+      inv_std == nullptr)
+    return NVN_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (channel_first || C == 1)
+    return run_rows(dtype, false, true, nullptr, x, gamma, beta, nullptr, nullptr, N * C, D, N,
+                    C, epsilon, y, mean, inv_std, nullptr, nullptr, workspace, workspace_bytes,
+                    s);
+  return run_nlc(dtype, false, nullptr, x, gamma, beta, nullptr, nullptr, N, C, D, epsilon, y,
+                 mean, inv_std, nullptr, nullptr, workspace, workspace_bytes, s);
+}
+
+int nvn_in_bwd(int dtype, const void* dy, const void* x, const float* gamma, const float* mean,
+               const float* inv_std, int64_t N, int64_t C, int64_t D, int channel_first,
+               void* dx, float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes,
+               void* stream) {
+  if (!valid_dtype(dtype) || N < 0 || C < 0 || D < 0) return NVN_ERR_INVALID_ARGUMENT;
+  if (C > 0 && (dgamma == nullptr || dbeta == nullptr)) return NVN_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (N == 0 || C == 0 || D == 0) return zero_grads(dgamma, dbeta, C, s);
+  if (dy == nullptr || x == nullptr || gamma == nullptr || mean == nullptr ||
+      inv_std == nullptr || dx == nullptr)
+    return NVN_ERR_INVALID_ARGUMENT;
+  if (channel_first || C == 1)
+    return run_rows(dtype, true, true, dy, x, gamma, nullptr, mean, inv_std, N * C, D, N, C,
+                    0.f, dx, nullptr, nullptr, dgamma, dbeta, workspace, workspace_bytes, s);
+  return run_nlc(dtype, true, dy, x, gamma, nullptr, mean, inv_std, N, C, D, 0.f, dx, nullptr,
+                 nullptr, dgamma, dbeta, workspace, workspace_bytes, s);
+}
+
+int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int channel_first,
+                      char* out, size_t out_bytes) {
+  if (out == nullptr || out_bytes == 0 || !valid_dtype(dtype) || op < 0 || op > 3)
+    return NVN_ERR_INVALID_ARGUMENT;
+  const bool bwd = (op & 1) != 0;
+  const bool is_in = op >= 2;
+  if (N <= 0 || D <= 0 || (is_in && C <= 0)) {
+    snprintf(out, out_bytes, "empty");
+    return NVN_OK;
+  }
+  if (is_in && !channel_first && C != 1) {
+    NlcPlan p;
+    int st = plan_nlc(dtype, bwd, N, C, D, true, &p);
+    if (st != NVN_OK) return st;
+    snprintf(out, out_bytes,
+             "nlc two-phase epv=%d cvt=%d lanes=%d ctiles=%d chunk=%lld nchunks=%d grid=%lld",
+             p.scalar ? 1 : full_epv(dtype), p.s2.cvt, p.s2.lanes, p.s2.ctiles,
+             static_cast<long long>(p.s2.chunk), p.s2.nchunks,
+             static_cast<long long>(p.s2.nchunks) * p.s2.ctiles * N);
+    return NVN_OK;
+  }
+  const int64_t rows = is_in ? N * C : N;
+  RowProblemPlan p;
+  int st = plan_rows(dtype, bwd, is_in, rows, D, N, is_in ? C : 1, true, &p);
+  if (st != NVN_OK) return st;
+  if (p.two_phase) {
+    snprintf(out, out_bytes, "rows two-phase epv=%d chunk=%lld nchunks=%d slices=%d",
+             p.scalar ? 1 : full_epv(dtype), static_cast<long long>(p.r2.chunk), p.r2.nchunks,
+             p.r2.slices);
+  } else {
+    snprintf(out, out_bytes, "rows tpr=%d vpt=%d cluster=%d epv=%d block=%d grid=%d",
+             p.rows.tpr, p.rows.vpt, p.rows.cluster, p.rows.epv, p.rows.block, p.rows.grid);
+  }
+  return NVN_OK;
+}
+
+}  // extern "C"

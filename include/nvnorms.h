@@ -1,0 +1,172 @@
+/*
+ * nvnorms.h - C ABI of libnvnorms: fused LayerNorm / InstanceNorm forward and
+ * gradient kernels for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a TensorFlow OpKernel (or any other host runtime) binds
+ * to.  It replaces the GPU functors of NVIDIA/atex's nv_norms package:
+ *
+ *   functor::FusedLayerNorm<GPUDevice,T,U>         atex/nv_norms/cc/kernels/fused_layer_norm_op.cu:805-893
+ *   functor::FusedLayerNormGrad<GPUDevice,T,U>     atex/nv_norms/cc/kernels/fused_layer_norm_op.cu:895-1030
+ *   functor::FusedInstanceNorm<GPUDevice,T,U>      atex/nv_norms/cc/kernels/fused_instance_norm_op.cu:1457-1517
+ *   functor::FusedInstanceNormGrad<GPUDevice,T,U>  atex/nv_norms/cc/kernels/fused_instance_norm_op.cu:1519-1561
+ *
+ * and the shape bookkeeping the OpKernels do before calling them
+ * (GetBatchAndFeatureSizes, atex/nv_norms/cc/kernels/fused_layer_norm_op.cc:252-282;
+ * FormatFromSuccinctString, atex/nv_norms/cc/kernels/fused_instance_norm_op.cc:25-34).
+ *
+ * Conventions
+ *   - Every function returns NVN_OK (0) or a negative nvn_status; nothing throws,
+ *     aborts, allocates device memory or synchronises the device or the stream.
+ *   - All device buffers (inputs, outputs, workspace) are owned by the caller and
+ *     must belong to the device that is current on the calling thread.
+ *   - Work is enqueued asynchronously on `stream` (a cudaStream_t passed as void*).
+ *   - T is the activation type named by `dtype`; gamma, beta, the saved statistics
+ *     and the parameter gradients are always fp32 (the reference's `U`).
+ *   - Pointers only need the natural alignment of their element type; the library
+ *     selects 128-bit vector kernels when the actual alignment allows it.
+ *   - `y` may alias `x` in the forward calls (the reference forwards its input
+ *     buffer to the output, fused_layer_norm_op.cc:337, fused_instance_norm_op.cc:390).
+ *   - The second saved statistic is 1/sqrt(var + epsilon) (the reference calls it
+ *     "inv_var", norm_util.h:255-258).
+ *   - Backward uses the mean / inverse-std passed in; it never recomputes them.
+ *   - Empty inputs (N*D == 0 or N*C*D == 0) launch nothing, except that backward
+ *     zero-fills dgamma / dbeta (the reference's CPU kernels do,
+ *     fused_layer_norm_op.cc:96-103; its GPU kernels leave them unwritten).
+ *   - Calls are re-entrant and thread-safe.
+ */
+#ifndef NVNORMS_H_
+#define NVNORMS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define NVN_API
+#else
+#define NVN_API __attribute__((visibility("default")))
+#endif
+
+typedef enum nvn_dtype {
+  NVN_F32 = 0,  /* float            (reference T = float)       */
+  NVN_F16 = 1,  /* IEEE half        (reference T = Eigen::half) */
+  NVN_BF16 = 2  /* bfloat16         (extension: not in the reference's T list, norm_ops.cc:155) */
+} nvn_dtype;
+
+typedef enum nvn_status {
+  NVN_OK = 0,
+  NVN_ERR_INVALID_ARGUMENT = -1, /* null pointer, negative size, unknown dtype        */
+  NVN_ERR_AXIS_RANGE = -2,       /* "axis contains invalid value"                      */
+  NVN_ERR_AXIS_NOT_PACKED = -3,  /* "axis is not packed from last dim."                */
+  NVN_ERR_DATA_FORMAT = -4,      /* "We only accept 'NC...' or 'N...C' data format"    */
+  NVN_ERR_RANK = -5,             /* rank below 1 (LayerNorm) or below 4 (InstanceNorm) */
+  NVN_ERR_WORKSPACE = -6,        /* workspace missing, misaligned or too small         */
+  NVN_ERR_CUDA = -7,             /* a CUDA runtime call failed (see nvn_last_cuda_error) */
+  NVN_ERR_UNSUPPORTED = -8,      /* size beyond what the kernels index                 */
+  NVN_ERR_LIMIT = -9             /* size beyond a fixed built-in capacity              */
+} nvn_status;
+
+/* Library version: major*10000 + minor*100 + patch. */
+NVN_API int nvn_version(void);
+
+/* Human-readable text for a status.  For the shape errors the text is the
+ * InvalidArgument message of the reference op. */
+NVN_API const char* nvn_status_string(int status);
+
+/* cudaError_t value of the most recent failing CUDA call on this thread (0 if none). */
+NVN_API int nvn_last_cuda_error(void);
+
+/* Number of kernel launches this library has issued in this process so far. */
+NVN_API uint64_t nvn_launch_count(void);
+
+/* ---- shape bookkeeping (host only, no CUDA) ------------------------------- */
+
+/* LayerNorm: normalise `axis` entries (negative allowed), require them to be the
+ * trailing dimensions, return N = product of the leading dims, D = product of
+ * the normalised dims.  Replaces GetBatchAndFeatureSizes
+ * (fused_layer_norm_op.cc:252-282, norm_ops.cc:18-52). */
+NVN_API int nvn_ln_dims(int rank, const int64_t* dims, int n_axis, const int* axis,
+                        int64_t* N, int64_t* D);
+
+/* InstanceNorm: parse `data_format` (accepted iff longer than 2 characters,
+ * starting with 'N', with 'C' second or last: "NC...", "N...C", "NCHW", "NDHWC"
+ * ...), require rank >= 4, return N, C, D = product of the spatial dims and
+ * whether channels come first.  Replaces FormatFromSuccinctString and the
+ * reshaping in FusedInstanceNormOp::Compute (fused_instance_norm_op.cc:25-34, 333-376). */
+NVN_API int nvn_in_dims(int rank, const int64_t* dims, const char* data_format,
+                        int64_t* N, int64_t* C, int64_t* D, int* channel_first);
+
+/* ---- workspace sizes -------------------------------------------------------
+ * Bytes of device scratch each call needs for the given problem on the current
+ * device (0 is possible).  The workspace must be 256-byte aligned.  Replaces
+ * the context->allocate_temp calls inside the reference functors
+ * (fused_layer_norm_op.cu:852-868, 925-935; fused_instance_norm_op.cu:1238-1250,
+ * 1326-1340, 1534-1545).  Contents on entry are ignored; nothing needs zeroing. */
+NVN_API size_t nvn_ln_fwd_workspace_bytes(int dtype, int64_t N, int64_t D);
+NVN_API size_t nvn_ln_bwd_workspace_bytes(int dtype, int64_t N, int64_t D);
+NVN_API size_t nvn_in_fwd_workspace_bytes(int dtype, int64_t N, int64_t C, int64_t D,
+                                          int channel_first);
+NVN_API size_t nvn_in_bwd_workspace_bytes(int dtype, int64_t N, int64_t C, int64_t D,
+                                          int channel_first);
+
+/* ---- LayerNorm --------------------------------------------------------------
+ * x, y: [N, D] of T, row-major.  gamma, beta: [D] fp32.  mean, inv_std: [N] fp32.
+ *   mean_i    = sum_j x_ij / D
+ *   inv_std_i = 1 / sqrt(sum_j (x_ij - mean_i)^2 / D + epsilon)
+ *   y_ij      = (x_ij - mean_i) * inv_std_i * gamma_j + beta_j
+ * Replaces FusedLayerNorm<GPUDevice> (fused_layer_norm_op.cu:805-893). */
+NVN_API int nvn_ln_fwd(int dtype, const void* x, const float* gamma, const float* beta,
+                       int64_t N, int64_t D, float epsilon, void* y, float* mean,
+                       float* inv_std, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
+/* dy, x, dx: [N, D] of T.  dgamma, dbeta: [D] fp32.
+ *   dgamma_j = sum_i dy_ij (x_ij - mean_i) inv_std_i      dbeta_j = sum_i dy_ij
+ *   dx_ij    = dy_ij gamma_j inv_std_i
+ *              + (2 (x_ij - mean_i) dL/dvar_i + dL/dmean_i) / D
+ *   dL/dvar_i  = sum_j dy_ij gamma_j (x_ij - mean_i) (-1/2) inv_std_i^3
+ *   dL/dmean_i = sum_j -dy_ij gamma_j inv_std_i
+ * (LnNorm::DxOp, DvarOp, DmeanOp: norm_util.h:343-421, 486-513.)  The column
+ * sums are formed in a fixed order: results are bit-identical run to run.
+ * Replaces FusedLayerNormGrad<GPUDevice> (fused_layer_norm_op.cu:895-1030). */
+NVN_API int nvn_ln_bwd(int dtype, const void* dy, const void* x, const float* gamma,
+                       const float* mean, const float* inv_std, int64_t N, int64_t D,
+                       void* dx, float* dgamma, float* dbeta, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
+/* ---- InstanceNorm -----------------------------------------------------------
+ * x, y: [N, C, D] (channel_first != 0, "NC...") or [N, D, C] ("N...C") of T.
+ * gamma, beta: [C] fp32.  mean, inv_std: [N, C] fp32.  Statistics are taken
+ * over D for every (n, c).
+ * Replaces FusedInstanceNorm<GPUDevice> (fused_instance_norm_op.cu:1457-1517). */
+NVN_API int nvn_in_fwd(int dtype, const void* x, const float* gamma, const float* beta,
+                       int64_t N, int64_t C, int64_t D, int channel_first, float epsilon,
+                       void* y, float* mean, float* inv_std, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
+/* dgamma_c = sum_{n,d} dy (x - mean_nc) inv_std_nc,  dbeta_c = sum_{n,d} dy,
+ * dx = (S2_nc (x - mean_nc) + S1_nc) / D + dy gamma_c inv_std_nc  with
+ * S1_nc = sum_d -dy inv_std gamma,  S2_nc = sum_d -dy inv_std^3 gamma (x - mean)
+ * (InNorm::DwStatFusedOp, DxFusedOp: norm_util.h:518-557, 590-617).
+ * Replaces FusedInstanceNormGrad<GPUDevice> (fused_instance_norm_op.cu:1519-1561). */
+NVN_API int nvn_in_bwd(int dtype, const void* dy, const void* x, const float* gamma,
+                       const float* mean, const float* inv_std, int64_t N, int64_t C,
+                       int64_t D, int channel_first, void* dx, float* dgamma,
+                       float* dbeta, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
+/* ---- introspection (for tests, benchmarks and profiles) ---------------------
+ * Writes a short description of the kernel variant the dispatcher would pick,
+ * e.g. "rows tpr=256 vpt=2 cluster=1 epv=8 grid=592".  op: 0 = ln_fwd,
+ * 1 = ln_bwd, 2 = in_fwd, 3 = in_bwd.  C and channel_first are ignored for
+ * LayerNorm.  No reference counterpart. */
+NVN_API int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D,
+                              int channel_first, char* out, size_t out_bytes);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+#endif /* NVNORMS_H_ */
