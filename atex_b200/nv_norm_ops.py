@@ -94,10 +94,16 @@ def _cuda_contig(t: torch.Tensor, name: str) -> torch.Tensor:
 
 
 def _param(t: torch.Tensor, name: str) -> torch.Tensor:
-    t = _cuda_contig(t, name)
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
     if t.dtype != torch.float32:
         raise TypeError(f"{name} must be float32 (attr U), got {t.dtype}")
     return t
+
+
+def _on_device(*named):
+    """Shape validation needs no GPU; this runs after it and insists on CUDA memory."""
+    return [_cuda_contig(t, name) for t, name in named]
 
 
 def _shape_str(t: torch.Tensor) -> str:
@@ -157,7 +163,6 @@ def fused_layer_norm_op(x, scale, offset, axis: Iterable[int] = (-1,), epsilon: 
     """
     _require(isinstance(x, torch.Tensor) and x.dim() > 0, "input must be at least 1-dimensional",
              _shape_str(x) if isinstance(x, torch.Tensor) else "")
-    x = _cuda_contig(x, "x")
     code = _dtype_code(x, "x")
     scale, offset = _param(scale, "scale"), _param(offset, "offset")
     axis = _axis_list(axis)
@@ -166,6 +171,7 @@ def fused_layer_norm_op(x, scale, offset, axis: Iterable[int] = (-1,), epsilon: 
              "of x, got ", scale.numel(), " and ", D)
     _require(offset.numel() == D, "offset must have the same number of elements as the features "
              "of x, got ", offset.numel(), " and ", D)
+    x, scale, offset = _on_device((x, "x"), (scale, "scale"), (offset, "offset"))
     if out is None:
         y = torch.empty_like(x)
     else:
@@ -192,8 +198,7 @@ def fused_layer_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_spac
              "input must be at least 1-dimensional", _shape_str(y_backprop))
     _require(isinstance(x, torch.Tensor) and x.dim() > 0, "input must be at least 1-dimensional",
              _shape_str(x))
-    x = _cuda_contig(x, "x")
-    dy = _cuda_contig(y_backprop, "y_backprop")
+    dy = y_backprop
     code = _dtype_code(x, "x")
     if dy.dtype != x.dtype:
         raise TypeError(f"y_backprop ({dy.dtype}) and x ({x.dtype}) must have the same dtype")
@@ -210,6 +215,8 @@ def fused_layer_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_spac
              "batches of x, got ", mean.numel(), " and ", N)
     _require(inv_std.numel() == N, "reserve_space_2 must have the same number of elements as the "
              "channels of x, got ", inv_std.numel(), " and ", N)
+    x, dy, scale, mean, inv_std = _on_device((x, "x"), (dy, "y_backprop"), (scale, "scale"),
+                                             (mean, "reserve_space_1"), (inv_std, "reserve_space_2"))
     dx = torch.empty_like(x)
     dgamma = torch.empty_like(scale)
     dbeta = torch.empty_like(scale)
@@ -229,7 +236,6 @@ def fused_instance_norm_op(x, scale, offset, data_format: str = "N...C", epsilon
     with the statistics of shape [N, C]."""
     _require(isinstance(x, torch.Tensor), "input must be a tensor")
     N, C, D, cf = _in_dims(x, data_format)
-    x = _cuda_contig(x, "x")
     code = _dtype_code(x, "x")
     scale, offset = _param(scale, "scale"), _param(offset, "offset")
     _require(scale.dim() == 1, "scale must be 1-dimensional", _shape_str(scale))
@@ -238,6 +244,7 @@ def fused_instance_norm_op(x, scale, offset, data_format: str = "N...C", epsilon
              "of x, got ", scale.numel(), " and ", C)
     _require(offset.numel() == C, "offset must have the same number of elements as the channels "
              "of x, got ", offset.numel(), " and ", C)
+    x, scale, offset = _on_device((x, "x"), (scale, "scale"), (offset, "offset"))
     if out is None:
         y = torch.empty_like(x)
     else:
@@ -264,8 +271,7 @@ def fused_instance_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_s
              "input must be at least 4-dimensional", _shape_str(y_backprop))
     _require(isinstance(x, torch.Tensor) and x.dim() > 1, "input must be at least 2-dimensional",
              _shape_str(x))
-    x = _cuda_contig(x, "x")
-    dy = _cuda_contig(y_backprop, "y_backprop")
+    dy = y_backprop
     code = _dtype_code(x, "x")
     if dy.dtype != x.dtype:
         raise TypeError(f"y_backprop ({dy.dtype}) and x ({x.dtype}) must have the same dtype")
@@ -283,6 +289,8 @@ def fused_instance_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_s
              "the batches*channels of x, got ", mean.numel(), " and ", N * C)
     _require(inv_std.numel() == N * C, "reserve_space_2 must have the same number of elements as "
              "the batches * channels of x, got ", inv_std.numel(), " and ", N * C)
+    x, dy, scale, mean, inv_std = _on_device((x, "x"), (dy, "y_backprop"), (scale, "scale"),
+                                             (mean, "reserve_space_1"), (inv_std, "reserve_space_2"))
     dx = torch.empty_like(x)
     dgamma = torch.empty_like(scale)
     dbeta = torch.empty_like(scale)

@@ -66,7 +66,7 @@ def main(ref_root: str) -> None:
     out = {}
     # LayerNorm: (x_shape, axis) from testFusedLayerNormOp / NonTypical / Brittle shape lists
     ln_cases = [
-        ((2, 16), (1,)), ((5, 256), (1,)), ((8, 1024), (-1,)), ((2, 11), (1,)), ((2, 31), (1,)),
+        ((2, 16), (1,)), ((5, 256), (1,)), ((4, 1024), (-1,)), ((2, 11), (1,)), ((2, 31), (1,)),
         ((2, 2003), (1,)), ((2, 3, 16), (2,)), ((12, 4, 2, 2), (1, 2, 3)), ((1, 4001), (1,)),
     ]
     for k, (shape, axis) in enumerate(ln_cases):
@@ -77,7 +77,9 @@ def main(ref_root: str) -> None:
         gshape = tuple(shape[a] for a in ax)
         gamma = rng.normal(size=gshape).astype(np.float32)
         mean, istd = moments64(x.astype(np.float64), ax, eps)
-        cache = {"mean": _TensorLike(mean.reshape(-1)), "istd": _TensorLike(istd.reshape(-1))}
+        # float32-rounded statistics, promoted so the reference function works in float64
+        cache = {"mean": _TensorLike(mean.reshape(-1).astype(np.float64)),
+                 "istd": _TensorLike(istd.reshape(-1).astype(np.float64))}
         dgamma, dbeta, dx = ln_grad(x.astype(np.float64), dy.astype(np.float64),
                                     gamma.astype(np.float64), cache, ax)
         p = f"ln{k}_"
@@ -90,7 +92,7 @@ def main(ref_root: str) -> None:
     in_cases = [
         (2, 32, (8, 8), True), (2, 32, (8, 8), False), (2, 32, (4, 4, 4), True),
         (2, 32, (4, 4, 4), False), (2, 3, (1, 11), True), (2, 3, (1, 11), False),
-        (2, 5, (3, 4), False), (2, 4, (61, 82), True), (1, 8, (1, 31), False),
+        (2, 5, (3, 4), False), (1, 3, (61, 82), True), (1, 8, (1, 31), False),
     ]
     for k, (N, C, sp, cf) in enumerate(in_cases):
         eps = 1e-3
