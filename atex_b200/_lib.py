@@ -9,7 +9,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libnvnorms.so")
+# NVN_LIB_PATH points experiments at an alternative build of the same library.
+LIB_PATH = os.environ.get("NVN_LIB_PATH") or os.path.join(_HERE, "libnvnorms.so")
 
 NVN_F32, NVN_F16, NVN_BF16 = 0, 1, 2
 

@@ -22,7 +22,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OBJDIR = os.path.join(CSRC, "build")
-LIB = os.path.join(HERE, "libnvnorms.so")
+LIB = os.environ.get("NVN_LIB_OUT") or os.path.join(HERE, "libnvnorms.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -30,6 +30,9 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-fvisibility=hidden",
     "-I", INCLUDE,
 ]
+# Extra compiler flags for experiments (for example a pre-included header that
+# overrides the shape tables); empty in normal builds.
+NVCC_FLAGS += os.environ.get("NVN_EXTRA_NVCC_FLAGS", "").split()
 
 
 def _units():

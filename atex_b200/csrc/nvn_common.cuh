@@ -13,6 +13,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 namespace nvn {
 
 namespace cg = cooperative_groups;
@@ -157,6 +159,114 @@ __device__ __forceinline__ void store_params(float* __restrict__ p, int64_t off,
 }
 
 // ---------------------------------------------------------------------------
+// Packed fp32 arithmetic.
+//
+// sm_100 executes add / mul / fma on two fp32 values per lane in one instruction
+// (fma.rn.f32x2 and friends, exposed as __ffma2_rn / __fadd2_rn / __fmul2_rn).
+// At B200's HBM bandwidth a 16-bit norm kernel only has ~20-30 issue slots per
+// element, so the element-wise math is written on float2 lanes (P2); the
+// scalar family (EPV == 1) uses the same code with plain floats (P1).
+// ---------------------------------------------------------------------------
+struct P2 {
+  using E = float2;
+  static __device__ __forceinline__ E bcast(float s) { return make_float2(s, s); }
+  static __device__ __forceinline__ E add(E a, E b) { return __fadd2_rn(a, b); }
+  static __device__ __forceinline__ E mul(E a, E b) { return __fmul2_rn(a, b); }
+  static __device__ __forceinline__ E fma(E a, E b, E c) { return __ffma2_rn(a, b, c); }
+  static __device__ __forceinline__ float hsum(E a) { return a.x + a.y; }
+};
+struct P1 {
+  using E = float;
+  static __device__ __forceinline__ E bcast(float s) { return s; }
+  static __device__ __forceinline__ E add(E a, E b) { return a + b; }
+  static __device__ __forceinline__ E mul(E a, E b) { return a * b; }
+  static __device__ __forceinline__ E fma(E a, E b, E c) { return fmaf(a, b, c); }
+  static __device__ __forceinline__ float hsum(E a) { return a; }
+};
+template <int EPV>
+struct MathSel {
+  using M = P2;
+  static constexpr int NE = EPV / 2;  // float2 lanes per vector
+};
+template <>
+struct MathSel<1> {
+  using M = P1;
+  static constexpr int NE = 1;
+};
+
+// Pack<T, EPV>  <->  fp32 lanes
+template <typename T, int EPV>
+__device__ __forceinline__ void unpack(const Pack<T, EPV>& p,
+                                       typename MathSel<EPV>::M::E (&out)[MathSel<EPV>::NE]) {
+  if constexpr (EPV == 1) {
+    out[0] = Cvt<T>::to_f32(p.v[0]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < EPV / 2; ++i) {
+      if constexpr (sizeof(T) == 4) {
+        out[i] = make_float2(p.v[2 * i], p.v[2 * i + 1]);
+      } else if constexpr (std::is_same<T, __half>::value) {
+        out[i] = __half22float2(*reinterpret_cast<const __half2*>(&p.v[2 * i]));
+      } else {
+        out[i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&p.v[2 * i]));
+      }
+    }
+  }
+}
+
+template <typename T, int EPV>
+__device__ __forceinline__ Pack<T, EPV> repack(
+    const typename MathSel<EPV>::M::E (&in)[MathSel<EPV>::NE]) {
+  Pack<T, EPV> p;
+  if constexpr (EPV == 1) {
+    p.v[0] = Cvt<T>::from_f32(in[0]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < EPV / 2; ++i) {
+      if constexpr (sizeof(T) == 4) {
+        p.v[2 * i] = in[i].x;
+        p.v[2 * i + 1] = in[i].y;
+      } else if constexpr (std::is_same<T, __half>::value) {
+        *reinterpret_cast<__half2*>(&p.v[2 * i]) = __float22half2_rn(in[i]);
+      } else {
+        *reinterpret_cast<__nv_bfloat162*>(&p.v[2 * i]) = __float22bfloat162_rn(in[i]);
+      }
+    }
+  }
+  return p;
+}
+
+// EPV consecutive fp32 parameters as math lanes
+template <int EPV>
+__device__ __forceinline__ void load_param_lanes(const float* __restrict__ p, int64_t off,
+                                                 typename MathSel<EPV>::M::E (&out)[MathSel<EPV>::NE]) {
+  float t[EPV];
+  load_params<EPV>(p, off, t);
+  if constexpr (EPV == 1) {
+    out[0] = t[0];
+  } else {
+#pragma unroll
+    for (int i = 0; i < EPV / 2; ++i) out[i] = make_float2(t[2 * i], t[2 * i + 1]);
+  }
+}
+
+template <int EPV>
+__device__ __forceinline__ void store_param_lanes(
+    float* __restrict__ p, int64_t off, const typename MathSel<EPV>::M::E (&in)[MathSel<EPV>::NE]) {
+  float t[EPV];
+  if constexpr (EPV == 1) {
+    t[0] = in[0];
+  } else {
+#pragma unroll
+    for (int i = 0; i < EPV / 2; ++i) {
+      t[2 * i] = in[i].x;
+      t[2 * i + 1] = in[i].y;
+    }
+  }
+  store_params<EPV>(p, off, t);
+}
+
+// ---------------------------------------------------------------------------
 // Row-group all-reduce (sum) of NV values.
 //
 // A "row group" is TPR consecutive threads of a CTA (TPR a power of two).  For
@@ -178,7 +288,7 @@ struct ReduceSmem {
 
 template <int NV, int TPR, int BLOCK, int CS>
 __device__ __forceinline__ void group_allreduce(float (&v)[NV], ReduceSmem<NV, BLOCK>& sm,
-                                                int& phase) {
+                                                int& phase, int warp, int lane) {
   constexpr int kShuffleSpan = TPR < 32 ? TPR : 32;
 #pragma unroll
   for (int off = kShuffleSpan / 2; off > 0; off >>= 1) {
@@ -187,8 +297,6 @@ __device__ __forceinline__ void group_allreduce(float (&v)[NV], ReduceSmem<NV, B
   }
   if constexpr (TPR > 32) {
     constexpr int WPR = TPR / 32;  // warps per row group
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
     if (lane == 0) {
 #pragma unroll
       for (int k = 0; k < NV; ++k) sm.warp_part[phase][k][warp] = v[k];
@@ -206,7 +314,7 @@ __device__ __forceinline__ void group_allreduce(float (&v)[NV], ReduceSmem<NV, B
   if constexpr (CS > 1) {
     static_assert(TPR == BLOCK, "a cluster shares one row, so the CTA is one row group");
     cg::cluster_group cluster = cg::this_cluster();
-    if (threadIdx.x == 0) {
+    if (warp == 0 && lane == 0) {
 #pragma unroll
       for (int k = 0; k < NV; ++k) sm.cta_total[phase][k] = v[k];
     }

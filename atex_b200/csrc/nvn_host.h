@@ -36,34 +36,46 @@ struct RowsPlan {
   int tpr;
   int vpt;
   int epv;
+  int rb;
   int partial_rows;  // rows of [2][D] dgamma/dbeta partials the backward kernel writes
 };
 
 int device_sm_count();
 void count_launch();
 
-// Row-group shapes (TPR threads per row, VPT vectors per thread, CS CTAs per
-// cluster), ordered by capacity TPR*VPT*CS vectors.  X(index, TPR, VPT, CS).
-// Forward keeps VPT*EPV values (+ gamma/beta) per thread, backward about twice
-// that plus the dgamma/dbeta accumulators, so backward uses more threads per row.
-#define NVN_ROW_SHAPES_FWD(X)                                                                \
-  X(0, 4, 1, 1)    X(1, 8, 1, 1)    X(2, 16, 1, 1)   X(3, 32, 1, 1)   X(4, 32, 2, 1)         \
-  X(5, 32, 4, 1)   X(6, 64, 2, 1)   X(7, 64, 4, 1)   X(8, 128, 2, 1)  X(9, 128, 4, 1)        \
-  X(10, 256, 2, 1) X(11, 256, 4, 1) X(12, 512, 2, 1) X(13, 512, 4, 1) X(14, 1024, 2, 1)      \
-  X(15, 512, 4, 2) X(16, 512, 4, 4) X(17, 256, 4, 8) X(18, 512, 4, 8) X(19, 512, 4, 16)      \
-  X(20, 512, 8, 16)
+// Row-group shapes: X(index, TPR, VPT, CS, RB, PR, MINB, PF)
+//   TPR threads per row, VPT vectors per thread, CS CTAs per cluster, RB rows in
+//   flight per row group, PR gamma/beta cached in registers, MINB minimum CTAs per
+//   SM requested from the compiler (0 = no request), PF software prefetch of the
+//   next row batch.
+// "Light" kernels keep only the row itself in registers (LayerNorm forward,
+// InstanceNorm forward/backward); "heavy" is LayerNorm backward, which adds the
+// per-column dgamma/dbeta accumulators and therefore spreads a row over more
+// threads.  Capacity of a shape is TPR*VPT*CS vectors; the dispatcher takes the
+// first entry (in listing order) among those of the smallest sufficient capacity.
+#ifndef NVN_ROW_SHAPES_LIGHT
+#define NVN_ROW_SHAPES_LIGHT(X)                                                              \
+  X(0, 4, 1, 1, 4, 1, 0, 1)     X(1, 8, 1, 1, 4, 1, 0, 1)     X(2, 16, 1, 1, 4, 1, 0, 1)     \
+  X(3, 32, 1, 1, 4, 1, 0, 1)    X(4, 32, 2, 1, 2, 1, 0, 1)    X(5, 32, 4, 1, 2, 1, 0, 1)     \
+  X(6, 128, 2, 1, 1, 1, 0, 1)   X(7, 256, 2, 1, 2, 1, 0, 1)   X(8, 256, 4, 1, 1, 0, 0, 1)    \
+  X(9, 512, 4, 1, 1, 0, 0, 1)   X(10, 512, 8, 1, 1, 0, 0, 1)  X(11, 256, 8, 4, 1, 0, 0, 1)   \
+  X(12, 512, 8, 4, 1, 0, 0, 1)  X(13, 512, 8, 8, 1, 0, 0, 1)  X(14, 512, 8, 16, 1, 0, 0, 1)
+#endif
 
-#define NVN_ROW_SHAPES_BWD(X)                                                                \
-  X(0, 4, 1, 1)    X(1, 8, 1, 1)    X(2, 16, 1, 1)   X(3, 32, 1, 1)   X(4, 32, 2, 1)         \
-  X(5, 64, 2, 1)   X(6, 128, 2, 1)  X(7, 256, 2, 1)  X(8, 512, 2, 1)  X(9, 256, 2, 4)        \
-  X(10, 512, 2, 2) X(11, 512, 2, 4) X(12, 256, 2, 8) X(13, 512, 2, 8) X(14, 512, 2, 16)      \
-  X(15, 512, 4, 16)
+#ifndef NVN_ROW_SHAPES_HEAVY
+#define NVN_ROW_SHAPES_HEAVY(X)                                                              \
+  X(0, 4, 1, 1, 2, 1, 0, 1)     X(1, 8, 1, 1, 2, 1, 0, 1)     X(2, 16, 1, 1, 2, 1, 0, 1)     \
+  X(3, 32, 1, 1, 2, 1, 0, 1)    X(4, 32, 2, 1, 2, 1, 0, 1)    X(5, 128, 1, 1, 2, 1, 0, 1)    \
+  X(6, 128, 2, 1, 2, 0, 0, 1)   X(7, 256, 2, 1, 2, 1, 0, 1)   X(8, 512, 2, 1, 1, 1, 0, 1)    \
+  X(9, 512, 2, 2, 1, 1, 0, 1)   X(10, 512, 2, 4, 1, 1, 0, 1)  X(11, 256, 4, 8, 1, 1, 0, 1)   \
+  X(12, 512, 2, 16, 1, 1, 0, 1) X(13, 512, 4, 16, 1, 0, 0, 1)
+#endif
 
 // Scalar (EPV == 1) rows only get a coarse subset: they exist for odd D and
 // misaligned buffers, where correctness matters more than the last GB/s.
 #define NVN_ROW_SHAPES_SCALAR(X)                                                             \
-  X(0, 8, 4, 1) X(1, 32, 8, 1) X(2, 256, 8, 1) X(3, 512, 8, 2) X(4, 512, 8, 8)               \
-  X(5, 512, 8, 16)
+  X(0, 8, 4, 1, 1, 0, 0, 0) X(1, 32, 8, 1, 1, 0, 0, 0) X(2, 256, 8, 1, 1, 0, 0, 0)                    \
+  X(3, 512, 8, 2, 1, 0, 0, 0) X(4, 512, 8, 8, 1, 0, 0, 0) X(5, 512, 8, 16, 1, 0, 0, 0)
 
 // One entry point per (dtype, direction) translation unit.  `scalar` selects
 // the EPV == 1 family, `row_affine` the InstanceNorm "NC..." parameter indexing.

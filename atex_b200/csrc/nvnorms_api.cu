@@ -31,13 +31,13 @@ std::atomic<int> g_sm_count{0};
 struct Shape {
   int tpr, vpt, cs;
 };
-#define X(I, TPR, VPT, CS) {TPR, VPT, CS},
-const Shape kFwdShapes[] = {NVN_ROW_SHAPES_FWD(X)};
-const Shape kBwdShapes[] = {NVN_ROW_SHAPES_BWD(X)};
+#define X(I, TPR, VPT, CS, RB, PR, MINB, PF) {TPR, VPT, CS},
+const Shape kLightShapes[] = {NVN_ROW_SHAPES_LIGHT(X)};
+const Shape kHeavyShapes[] = {NVN_ROW_SHAPES_HEAVY(X)};
 const Shape kScalarShapes[] = {NVN_ROW_SHAPES_SCALAR(X)};
 #undef X
-constexpr int kNumFwd = sizeof(kFwdShapes) / sizeof(Shape);
-constexpr int kNumBwd = sizeof(kBwdShapes) / sizeof(Shape);
+constexpr int kNumLight = sizeof(kLightShapes) / sizeof(Shape);
+constexpr int kNumHeavy = sizeof(kHeavyShapes) / sizeof(Shape);
 constexpr int kNumScalar = sizeof(kScalarShapes) / sizeof(Shape);
 
 inline int64_t cap(const Shape& s) { return static_cast<int64_t>(s.tpr) * s.vpt * s.cs; }
@@ -108,8 +108,9 @@ int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int
   p->scalar = !(vec_ok && D % V == 0);
   const int epv = p->scalar ? 1 : V;
   const int64_t nvec = D / epv;
-  const Shape* table = p->scalar ? kScalarShapes : (bwd ? kBwdShapes : kFwdShapes);
-  const int ntab = p->scalar ? kNumScalar : (bwd ? kNumBwd : kNumFwd);
+  const bool heavy = bwd && !row_affine;
+  const Shape* table = p->scalar ? kScalarShapes : (heavy ? kHeavyShapes : kLightShapes);
+  const int ntab = p->scalar ? kNumScalar : (heavy ? kNumHeavy : kNumLight);
   const char* env = p->scalar ? nullptr : (bwd ? "NVN_FORCE_BWD_SHAPE" : "NVN_FORCE_FWD_SHAPE");
   p->shape = pick_shape(table, ntab, nvec, env);
   p->two_phase = p->shape < 0;
@@ -529,8 +530,9 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
              p.scalar ? 1 : full_epv(dtype), static_cast<long long>(p.r2.chunk), p.r2.nchunks,
              p.r2.slices);
   } else {
-    snprintf(out, out_bytes, "rows tpr=%d vpt=%d cluster=%d epv=%d block=%d grid=%d",
-             p.rows.tpr, p.rows.vpt, p.rows.cluster, p.rows.epv, p.rows.block, p.rows.grid);
+    snprintf(out, out_bytes, "rows tpr=%d vpt=%d cluster=%d rb=%d epv=%d block=%d grid=%d",
+             p.rows.tpr, p.rows.vpt, p.rows.cluster, p.rows.rb, p.rows.epv, p.rows.block,
+             p.rows.grid);
   }
   return NVN_OK;
 }

@@ -24,6 +24,8 @@
 //     (atex/nv_norms/cc/kernels/fused_instance_norm_op.cu:959-1003, 1167-1194, 169-250, 315-366)
 #pragma once
 
+#include <stdlib.h>
+
 #include "nvn_common.cuh"
 #include "nvn_host.h"
 
@@ -35,131 +37,203 @@ struct RowBlock {
   static constexpr int kRowsPerCta = kBlock / TPR;
 };
 
+// Template parameters shared by the forward and backward kernels
+//   EPV   elements per vector access (16 bytes / sizeof(T), or 1 for the scalar family)
+//   TPR   threads per row inside one CTA
+//   VPT   vectors per thread and row
+//   CS    CTAs per cluster (all working on the same row)
+//   RB    rows a row group works on at once: their loads are issued back to back and
+//         their reductions share one barrier
+//   PR    keep gamma (and beta) for the thread's columns in registers for the whole
+//         kernel instead of re-reading them (L1 / L2 hits) for every row
+//   MINB  minimum resident CTAs per SM asked of the compiler (register cap)
+//   PF    software prefetch: the loads of the next row batch are issued as soon as the
+//         current batch has been converted to fp32, so they are in flight during the
+//         reductions and the stores
+//
+// All element-wise math runs on fp32x2 lanes (nvn::P2) when EPV is even.
+
+//   EXACT the row is exactly TPR*VPT*CS vectors wide: no per-vector bounds checks
+//
+// Instruction count matters as much as bytes here: at ~23 bytes per clock per SM a
+// 16-bit row leaves ~20-30 issue slots per element.  Hence fp32x2 math, pointer
+// arithmetic that leaves only immediate offsets inside the vector loops, 1/D and
+// rsqrt instead of divisions, and the EXACT specialisation.
+
+template <typename T, int EPV, int VPT, int RB>
+struct RowTile {
+  Pack<T, EPV> p[RB][VPT];
+};
+
+// Loads the RB x VPT vectors of one row batch.  `src` already points at this
+// thread's first vector of row 0; rows are `rowvecs` vectors apart and a thread's
+// vectors VSTRIDE apart (a compile-time constant, so they become immediate offsets).
+template <typename T, int EPV, int VPT, int RB, int RPC, int VSTRIDE, bool EXACT>
+__device__ __forceinline__ void load_tile(const Pack<T, EPV>* __restrict__ src, int64_t row_first,
+                                          int64_t N, int64_t rowvecs, int nvalid,
+                                          RowTile<T, EPV, VPT, RB>& t) {
+#pragma unroll
+  for (int r = 0; r < RB; ++r) {
+    const int64_t row = row_first + r * RPC;
+    const Pack<T, EPV>* rp = src + row * rowvecs;
+    const bool rv = row < N;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      if (rv && (EXACT || v < nvalid)) {
+        t.p[r][v] = load_stream<T, EPV>(reinterpret_cast<const T*>(rp + v * VSTRIDE), 0);
+      } else {
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) t.p[r][v].v[e] = Cvt<T>::from_f32(0.f);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------
-template <typename T, int EPV, int VPT, int TPR, int CS, bool ROW_AFFINE>
-__global__ void __launch_bounds__(RowBlock<TPR>::kBlock)
+template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, bool PF,
+          bool EXACT, bool ROW_AFFINE>
+__global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
     rows_fwd_kernel(const RowsArgs a) {
   constexpr int BLOCK = RowBlock<TPR>::kBlock;
   constexpr int RPC = RowBlock<TPR>::kRowsPerCta;
+  constexpr int VSTRIDE = TPR * CS;
   static_assert(CS == 1 || RPC == 1, "cluster kernels own one row per cluster");
-  constexpr bool PARAMS_IN_REGS = !ROW_AFFINE && (VPT * EPV <= 32);
+  constexpr bool PARAMS_IN_REGS = !ROW_AFFINE && PR;
+  using M = typename MathSel<EPV>::M;
+  using E = typename M::E;
+  constexpr int NE = MathSel<EPV>::NE;
+  using P = Pack<T, EPV>;
 
-  __shared__ ReduceSmem<1, BLOCK> sm;
+  __shared__ ReduceSmem<RB, BLOCK> sm;
   int phase = 0;
 
-  // y may alias x (in-place forward), so neither pointer is __restrict__.
-  const T* x = static_cast<const T*>(a.x);
-  T* y = static_cast<T*>(a.out);
   const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
   const int group = tid / TPR;
   const int lir = tid % TPR;
   unsigned crank = 0;
   if constexpr (CS > 1) crank = cg::this_cluster().block_rank();
   const int64_t unit = blockIdx.x / CS;
   const int64_t nunits = gridDim.x / CS;
-  const int64_t D = a.D;
-  const int nvec = static_cast<int>(D / EPV);
-  const float fD = static_cast<float>(D);
-
-  int col[VPT];
-#pragma unroll
-  for (int v = 0; v < VPT; ++v) {
-    const int vi = v * (TPR * CS) + static_cast<int>(crank) * TPR + lir;
-    col[v] = vi < nvec ? vi * EPV : -1;
+  const int64_t N = a.N;
+  const int64_t rowvecs = a.D / EPV;
+  const float inv_D = 1.0f / static_cast<float>(a.D);
+  const float eps = a.eps;
+  const int vec0 = static_cast<int>(crank) * TPR + lir;
+  // number of this thread's vectors that fall inside the row (all VPT when EXACT)
+  int nvalid = VPT;
+  if constexpr (!EXACT) {
+    const int left = static_cast<int>(rowvecs) - vec0;
+    nvalid = left <= 0 ? 0 : (left + VSTRIDE - 1) / VSTRIDE;
+    nvalid = nvalid > VPT ? VPT : nvalid;
   }
+  // y may alias x (in-place forward), so these are not __restrict__.
+  const P* xp = reinterpret_cast<const P*>(a.x) + vec0;
+  P* yp = reinterpret_cast<P*>(a.out) + vec0;
 
-  float g[PARAMS_IN_REGS ? VPT : 1][EPV], b[PARAMS_IN_REGS ? VPT : 1][EPV];
+  E g[PARAMS_IN_REGS ? VPT : 1][NE], b[PARAMS_IN_REGS ? VPT : 1][NE];
   if constexpr (PARAMS_IN_REGS) {
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
-      if (col[v] >= 0) {
-        load_params<EPV>(a.gamma, col[v], g[v]);
-        load_params<EPV>(a.beta, col[v], b[v]);
+      if (EXACT || v < nvalid) {
+        load_param_lanes<EPV>(a.gamma, static_cast<int64_t>(vec0 + v * VSTRIDE) * EPV, g[v]);
+        load_param_lanes<EPV>(a.beta, static_cast<int64_t>(vec0 + v * VSTRIDE) * EPV, b[v]);
       } else {
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) g[v][e] = b[v][e] = 0.f;
+        for (int e = 0; e < NE; ++e) g[v][e] = b[v][e] = M::bcast(0.f);
       }
     }
   }
 
-  for (int64_t row0 = unit * RPC; row0 < a.N; row0 += nunits * RPC) {
-    const int64_t row = row0 + group;
-    const bool rv = row < a.N;
-    const int64_t base = row * D;
+  const int64_t stride = nunits * (RPC * RB);
+  const int64_t first = unit * (RPC * RB) + group;
+  RowTile<T, EPV, VPT, RB> tile;
+  if constexpr (PF) load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, first, N, rowvecs, nvalid, tile);
+  for (int64_t row0 = first; row0 - group < N; row0 += stride) {
+    if constexpr (!PF)
+      load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, row0, N, rowvecs, nvalid, tile);
 
-    float xf[VPT][EPV];
+    E xv[RB][VPT][NE];
+    float s[RB];
 #pragma unroll
-    for (int v = 0; v < VPT; ++v) {
-      if (rv && col[v] >= 0) {
-        const Pack<T, EPV> p = load_stream<T, EPV>(x, base + col[v]);
+    for (int r = 0; r < RB; ++r) {
+      E acc = M::bcast(0.f);
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) xf[v][e] = Cvt<T>::to_f32(p.v[e]);
-      } else {
+      for (int v = 0; v < VPT; ++v) {
+        unpack<T, EPV>(tile.p[r][v], xv[r][v]);
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) xf[v][e] = 0.f;
+        for (int e = 0; e < NE; ++e) acc = M::add(acc, xv[r][v][e]);
       }
+      s[r] = M::hsum(acc);
     }
+    if constexpr (PF)
+      load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, row0 + stride, N, rowvecs, nvalid, tile);
+    group_allreduce<RB, TPR, BLOCK, CS>(s, sm, phase, warp, lane);
 
-    float s[1] = {0.f};
+    float mean[RB], q[RB];
 #pragma unroll
-    for (int v = 0; v < VPT; ++v)
+    for (int r = 0; r < RB; ++r) {
+      mean[r] = s[r] * inv_D;
+      const E nm = M::bcast(-mean[r]);
+      E acc = M::bcast(0.f);
 #pragma unroll
-      for (int e = 0; e < EPV; ++e) s[0] += xf[v][e];
-    group_allreduce<1, TPR, BLOCK, CS>(s, sm, phase);
-    const float mean = s[0] / fD;
-
-    float q[1] = {0.f};
+      for (int v = 0; v < VPT; ++v) {
+        if (EXACT || v < nvalid) {
 #pragma unroll
-    for (int v = 0; v < VPT; ++v) {
-      if (col[v] >= 0) {
-#pragma unroll
-        for (int e = 0; e < EPV; ++e) {
-          const float d = xf[v][e] - mean;
-          q[0] = fmaf(d, d, q[0]);
+          for (int e = 0; e < NE; ++e) {
+            xv[r][v][e] = M::add(xv[r][v][e], nm);  // centred value, reused below
+            acc = M::fma(xv[r][v][e], xv[r][v][e], acc);
+          }
         }
       }
+      q[r] = M::hsum(acc);
     }
-    group_allreduce<1, TPR, BLOCK, CS>(q, sm, phase);
-    const float ivar = 1.0f / sqrtf(q[0] / fD + a.eps);
-
-    float gr = 1.f, br = 0.f;
-    if constexpr (ROW_AFFINE) {
-      if (rv) {
-        const int64_t c = row % a.C;
-        gr = __ldg(a.gamma + c);
-        br = __ldg(a.beta + c);
-      }
-    }
+    group_allreduce<RB, TPR, BLOCK, CS>(q, sm, phase, warp, lane);
 
 #pragma unroll
-    for (int v = 0; v < VPT; ++v) {
-      if (rv && col[v] >= 0) {
-        Pack<T, EPV> o;
+    for (int r = 0; r < RB; ++r) {
+      const int64_t row = row0 + r * RPC;
+      const float ivar = rsqrtf(fmaf(q[r], inv_D, eps));
+      if (row < N) {
+        float gr = 1.f, br = 0.f;
         if constexpr (ROW_AFFINE) {
-          const float sc = ivar * gr;
-#pragma unroll
-          for (int e = 0; e < EPV; ++e)
-            o.v[e] = Cvt<T>::from_f32(fmaf(xf[v][e] - mean, sc, br));
-        } else if constexpr (PARAMS_IN_REGS) {
-#pragma unroll
-          for (int e = 0; e < EPV; ++e)
-            o.v[e] = Cvt<T>::from_f32(fmaf((xf[v][e] - mean) * ivar, g[v][e], b[v][e]));
-        } else {
-          float gg[EPV], bb[EPV];
-          load_params<EPV>(a.gamma, col[v], gg);
-          load_params<EPV>(a.beta, col[v], bb);
-#pragma unroll
-          for (int e = 0; e < EPV; ++e)
-            o.v[e] = Cvt<T>::from_f32(fmaf((xf[v][e] - mean) * ivar, gg[e], bb[e]));
+          const int64_t c = row % a.C;
+          gr = __ldg(a.gamma + c);
+          br = __ldg(a.beta + c);
         }
-        store_stream<T, EPV>(y, base + col[v], o);
+        const E iv2 = M::bcast(ivar);
+        const E sc2 = M::bcast(ivar * gr);
+        const E br2 = M::bcast(br);
+        P* rp = yp + row * rowvecs;
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+          if (EXACT || v < nvalid) {
+            E o[NE];
+            if constexpr (ROW_AFFINE) {
+#pragma unroll
+              for (int e = 0; e < NE; ++e) o[e] = M::fma(xv[r][v][e], sc2, br2);
+            } else if constexpr (PARAMS_IN_REGS) {
+#pragma unroll
+              for (int e = 0; e < NE; ++e)
+                o[e] = M::fma(M::mul(xv[r][v][e], iv2), g[v][e], b[v][e]);
+            } else {
+              E gg[NE], bb[NE];
+              load_param_lanes<EPV>(a.gamma, static_cast<int64_t>(vec0 + v * VSTRIDE) * EPV, gg);
+              load_param_lanes<EPV>(a.beta, static_cast<int64_t>(vec0 + v * VSTRIDE) * EPV, bb);
+#pragma unroll
+              for (int e = 0; e < NE; ++e) o[e] = M::fma(M::mul(xv[r][v][e], iv2), gg[e], bb[e]);
+            }
+            store_stream<T, EPV>(reinterpret_cast<T*>(rp + v * VSTRIDE), 0, repack<T, EPV>(o));
+          }
+        }
+        if (lir == 0 && crank == 0) {
+          a.mean[row] = mean[r];
+          a.ivar[row] = ivar;
+        }
       }
-    }
-    if (rv && lir == 0 && crank == 0) {
-      a.mean[row] = mean;
-      a.ivar[row] = ivar;
     }
   }
   // A CTA's shared memory must stay mapped until its cluster peers have read it.
@@ -169,50 +243,59 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock)
 // ---------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------
-template <typename T, int EPV, int VPT, int TPR, int CS, bool ROW_AFFINE>
-__global__ void __launch_bounds__(RowBlock<TPR>::kBlock)
+template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, bool PF,
+          bool EXACT, bool ROW_AFFINE>
+__global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
     rows_bwd_kernel(const RowsArgs a) {
   constexpr int BLOCK = RowBlock<TPR>::kBlock;
   constexpr int RPC = RowBlock<TPR>::kRowsPerCta;
+  constexpr int VSTRIDE = TPR * CS;
   static_assert(CS == 1 || RPC == 1, "cluster kernels own one row per cluster");
-  constexpr bool PARAMS_IN_REGS = !ROW_AFFINE && (VPT * EPV <= 16);
+  constexpr bool PARAMS_IN_REGS = !ROW_AFFINE && PR;
   constexpr int CAP = TPR * VPT * EPV;  // columns one row group covers (CS == 1)
+  using M = typename MathSel<EPV>::M;
+  using E = typename M::E;
+  constexpr int NE = MathSel<EPV>::NE;
+  using P = Pack<T, EPV>;
 
-  __shared__ ReduceSmem<2, BLOCK> sm;
+  __shared__ ReduceSmem<2 * RB, BLOCK> sm;
   __shared__ float comb[(!ROW_AFFINE && RPC > 1) ? 2 * CAP : 1];
   int phase = 0;
 
-  const T* __restrict__ x = static_cast<const T*>(a.x);
-  const T* __restrict__ dy = static_cast<const T*>(a.dy);
-  T* __restrict__ dx = static_cast<T*>(a.out);
   const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
   const int group = tid / TPR;
   const int lir = tid % TPR;
   unsigned crank = 0;
   if constexpr (CS > 1) crank = cg::this_cluster().block_rank();
   const int64_t unit = blockIdx.x / CS;
   const int64_t nunits = gridDim.x / CS;
+  const int64_t N = a.N;
   const int64_t D = a.D;
-  const int nvec = static_cast<int>(D / EPV);
+  const int64_t rowvecs = D / EPV;
   const float inv_D = 1.0f / static_cast<float>(D);
-
-  int col[VPT];
-#pragma unroll
-  for (int v = 0; v < VPT; ++v) {
-    const int vi = v * (TPR * CS) + static_cast<int>(crank) * TPR + lir;
-    col[v] = vi < nvec ? vi * EPV : -1;
+  const int vec0 = static_cast<int>(crank) * TPR + lir;
+  int nvalid = VPT;
+  if constexpr (!EXACT) {
+    const int left = static_cast<int>(rowvecs) - vec0;
+    nvalid = left <= 0 ? 0 : (left + VSTRIDE - 1) / VSTRIDE;
+    nvalid = nvalid > VPT ? VPT : nvalid;
   }
+  const P* __restrict__ xp = reinterpret_cast<const P*>(a.x) + vec0;
+  const P* __restrict__ dyp = reinterpret_cast<const P*>(a.dy) + vec0;
+  P* __restrict__ dxp = reinterpret_cast<P*>(a.out) + vec0;
 
-  float g[PARAMS_IN_REGS ? VPT : 1][EPV];
-  float dg[ROW_AFFINE ? 1 : VPT][EPV], db[ROW_AFFINE ? 1 : VPT][EPV];
+  E g[PARAMS_IN_REGS ? VPT : 1][NE];
+  E dg[ROW_AFFINE ? 1 : VPT][NE], db[ROW_AFFINE ? 1 : VPT][NE];
   if constexpr (PARAMS_IN_REGS) {
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
-      if (col[v] >= 0) {
-        load_params<EPV>(a.gamma, col[v], g[v]);
+      if (EXACT || v < nvalid) {
+        load_param_lanes<EPV>(a.gamma, static_cast<int64_t>(vec0 + v * VSTRIDE) * EPV, g[v]);
       } else {
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) g[v][e] = 0.f;
+        for (int e = 0; e < NE; ++e) g[v][e] = M::bcast(0.f);
       }
     }
   }
@@ -220,84 +303,100 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock)
 #pragma unroll
     for (int v = 0; v < VPT; ++v)
 #pragma unroll
-      for (int e = 0; e < EPV; ++e) dg[v][e] = db[v][e] = 0.f;
+      for (int e = 0; e < NE; ++e) dg[v][e] = db[v][e] = M::bcast(0.f);
   }
 
-  for (int64_t row0 = unit * RPC; row0 < a.N; row0 += nunits * RPC) {
-    const int64_t row = row0 + group;
-    const bool rv = row < a.N;
-    const int64_t base = row * D;
-
-    Pack<T, EPV> px[VPT], pdy[VPT];
-#pragma unroll
-    for (int v = 0; v < VPT; ++v) {
-      if (rv && col[v] >= 0) {
-        px[v] = load_stream<T, EPV>(x, base + col[v]);
-        pdy[v] = load_stream<T, EPV>(dy, base + col[v]);
-      }
+  const int64_t stride = nunits * (RPC * RB);
+  const int64_t first = unit * (RPC * RB) + group;
+  RowTile<T, EPV, VPT, RB> tx, tdy;
+  if constexpr (PF) {
+    load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, first, N, rowvecs, nvalid, tx);
+    load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(dyp, first, N, rowvecs, nvalid, tdy);
+  }
+  for (int64_t row0 = first; row0 - group < N; row0 += stride) {
+    if constexpr (!PF) {
+      load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, row0, N, rowvecs, nvalid, tx);
+      load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(dyp, row0, N, rowvecs, nvalid, tdy);
     }
-    float mean = 0.f, ivar = 0.f;
-    if (rv) {
-      mean = __ldg(a.mean_in + row);
-      ivar = __ldg(a.ivar_in + row);
-    }
-
-    // xh = (x - mean) * ivar ; gy = dy * gamma (LayerNorm) or dy (row-affine)
-    float xh[VPT][EPV], gy[VPT][EPV];
-    float r[2] = {0.f, 0.f};
+    float ivar[RB];
+    // xh = (x - mean) * ivar ; gy = dy * gamma (LayerNorm) or dy (row-affine, where
+    // gamma is a per-row scalar applied at the end).  red = (sum gy, sum gy * xh).
+    E xh[RB][VPT][NE], gy[RB][VPT][NE];
+    float red[2 * RB];
 #pragma unroll
-    for (int v = 0; v < VPT; ++v) {
-      if (rv && col[v] >= 0) {
-        float gg[EPV];
-        if constexpr (!ROW_AFFINE && !PARAMS_IN_REGS) load_params<EPV>(a.gamma, col[v], gg);
+    for (int r = 0; r < RB; ++r) {
+      const int64_t row = row0 + r * RPC;
+      const bool rv = row < N;
+      const float mean = rv ? __ldg(a.mean_in + row) : 0.f;
+      ivar[r] = rv ? __ldg(a.ivar_in + row) : 0.f;
+      const E nm = M::bcast(-mean), iv2 = M::bcast(ivar[r]);
+      E r0 = M::bcast(0.f), r1 = M::bcast(0.f);
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) {
-          const float xv = (Cvt<T>::to_f32(px[v].v[e]) - mean) * ivar;
-          const float dv = Cvt<T>::to_f32(pdy[v].v[e]);
-          xh[v][e] = xv;
-          if constexpr (ROW_AFFINE) {
-            gy[v][e] = dv;
-          } else {
-            dg[v][e] = fmaf(dv, xv, dg[v][e]);
-            db[v][e] += dv;
-            if constexpr (PARAMS_IN_REGS) {
-              gy[v][e] = dv * g[v][e];
-            } else {
-              gy[v][e] = dv * gg[e];
+      for (int v = 0; v < VPT; ++v) {
+        unpack<T, EPV>(tx.p[r][v], xh[r][v]);
+        unpack<T, EPV>(tdy.p[r][v], gy[r][v]);
+        if (EXACT || v < nvalid) {
+          E gg[NE];
+          if constexpr (!ROW_AFFINE && !PARAMS_IN_REGS)
+            load_param_lanes<EPV>(a.gamma, static_cast<int64_t>(vec0 + v * VSTRIDE) * EPV, gg);
+#pragma unroll
+          for (int e = 0; e < NE; ++e) {
+            xh[r][v][e] = M::mul(M::add(xh[r][v][e], nm), iv2);
+            if constexpr (!ROW_AFFINE) {
+              dg[v][e] = M::fma(gy[r][v][e], xh[r][v][e], dg[v][e]);
+              db[v][e] = M::add(db[v][e], gy[r][v][e]);
+              if constexpr (PARAMS_IN_REGS) {
+                gy[r][v][e] = M::mul(gy[r][v][e], g[v][e]);
+              } else {
+                gy[r][v][e] = M::mul(gy[r][v][e], gg[e]);
+              }
             }
+            r0 = M::add(r0, gy[r][v][e]);
+            r1 = M::fma(gy[r][v][e], xh[r][v][e], r1);
           }
-          r[0] += gy[v][e];
-          r[1] = fmaf(gy[v][e], xv, r[1]);
         }
-      } else {
-#pragma unroll
-        for (int e = 0; e < EPV; ++e) xh[v][e] = gy[v][e] = 0.f;
       }
+      red[2 * r] = M::hsum(r0);
+      red[2 * r + 1] = M::hsum(r1);
     }
-    group_allreduce<2, TPR, BLOCK, CS>(r, sm, phase);
+    if constexpr (PF) {
+      load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, row0 + stride, N, rowvecs, nvalid, tx);
+      load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(dyp, row0 + stride, N, rowvecs, nvalid, tdy);
+    }
+    group_allreduce<2 * RB, TPR, BLOCK, CS>(red, sm, phase, warp, lane);
 
-    float scale = ivar;
-    if constexpr (ROW_AFFINE) {
-      if (rv) {
-        const int64_t n = row / a.C;
-        const int64_t c = row - n * a.C;
-        scale = ivar * __ldg(a.gamma + c);
-        if (lir == 0 && crank == 0) {
-          // per-(n, c) partials laid out [n][2][C]: dgamma then dbeta
-          a.ws[(n * 2 + 0) * a.C + c] = r[1];
-          a.ws[(n * 2 + 1) * a.C + c] = r[0];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      const int64_t row = row0 + r * RPC;
+      if (row < N) {
+        float scale = ivar[r];
+        if constexpr (ROW_AFFINE) {
+          const int64_t n = row / a.C;
+          const int64_t c = row - n * a.C;
+          scale = ivar[r] * __ldg(a.gamma + c);
+          if (lir == 0 && crank == 0) {
+            // per-(n, c) partials laid out [n][2][C]: dgamma then dbeta
+            a.ws[(n * 2 + 0) * a.C + c] = red[2 * r + 1];
+            a.ws[(n * 2 + 1) * a.C + c] = red[2 * r];
+          }
         }
-      }
-    }
-    const float m0 = r[0] * inv_D, m1 = r[1] * inv_D;
+        // dx = scale * (gy - (m0 + xh * m1)), m0 = red0 / D, m1 = red1 / D.  The
+        // subtraction happens before the scaling so that rows whose terms cancel
+        // exactly (D == 1, constant rows) give exactly zero.
+        const E sc2 = M::bcast(scale);
+        const E nm0 = M::bcast(-(red[2 * r] * inv_D));
+        const E nm1 = M::bcast(-(red[2 * r + 1] * inv_D));
+        P* rp = dxp + row * rowvecs;
 #pragma unroll
-    for (int v = 0; v < VPT; ++v) {
-      if (rv && col[v] >= 0) {
-        Pack<T, EPV> o;
+        for (int v = 0; v < VPT; ++v) {
+          if (EXACT || v < nvalid) {
+            E o[NE];
 #pragma unroll
-        for (int e = 0; e < EPV; ++e)
-          o.v[e] = Cvt<T>::from_f32(scale * (gy[v][e] - fmaf(xh[v][e], m1, m0)));
-        store_stream<T, EPV>(dx, base + col[v], o);
+            for (int e = 0; e < NE; ++e)
+              o[e] = M::mul(M::add(gy[r][v][e], M::fma(xh[r][v][e], nm1, nm0)), sc2);
+            store_stream<T, EPV>(reinterpret_cast<T*>(rp + v * VSTRIDE), 0, repack<T, EPV>(o));
+          }
+        }
       }
     }
   }
@@ -307,19 +406,27 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock)
     float* __restrict__ wb = a.ws + (unit * 2 + 1) * D;
     if constexpr (RPC > 1) {
       // Fold the row groups of this CTA in group order, then group 0 writes.
+      float* cg_ = comb;
+      float* cb_ = comb + CAP;
       for (int rgrp = 0; rgrp < RPC; ++rgrp) {
         if (group == rgrp) {
 #pragma unroll
           for (int v = 0; v < VPT; ++v)
 #pragma unroll
-            for (int e = 0; e < EPV; ++e) {
-              const int idx = (v * EPV + e) * TPR + lir;
-              if (rgrp == 0) {
-                comb[idx] = dg[v][e];
-                comb[CAP + idx] = db[v][e];
+            for (int e = 0; e < NE; ++e) {
+              // lane-major layout keeps the shared-memory accesses conflict-free
+              if constexpr (EPV == 1) {
+                const int idx = v * TPR + lir;
+                cg_[idx] = (rgrp == 0 ? 0.f : cg_[idx]) + dg[v][e];
+                cb_[idx] = (rgrp == 0 ? 0.f : cb_[idx]) + db[v][e];
               } else {
-                comb[idx] += dg[v][e];
-                comb[CAP + idx] += db[v][e];
+                float2* cg2 = reinterpret_cast<float2*>(cg_);
+                float2* cb2 = reinterpret_cast<float2*>(cb_);
+                const int idx = (v * NE + e) * TPR + lir;
+                float2 pg = rgrp == 0 ? make_float2(0.f, 0.f) : cg2[idx];
+                float2 pb = rgrp == 0 ? make_float2(0.f, 0.f) : cb2[idx];
+                cg2[idx] = make_float2(pg.x + dg[v][e].x, pg.y + dg[v][e].y);
+                cb2[idx] = make_float2(pb.x + db[v][e].x, pb.y + db[v][e].y);
               }
             }
         }
@@ -329,19 +436,23 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock)
 #pragma unroll
         for (int v = 0; v < VPT; ++v)
 #pragma unroll
-          for (int e = 0; e < EPV; ++e) {
-            const int idx = (v * EPV + e) * TPR + lir;
-            dg[v][e] = comb[idx];
-            db[v][e] = comb[CAP + idx];
+          for (int e = 0; e < NE; ++e) {
+            if constexpr (EPV == 1) {
+              dg[v][e] = cg_[v * TPR + lir];
+              db[v][e] = cb_[v * TPR + lir];
+            } else {
+              dg[v][e] = reinterpret_cast<float2*>(cg_)[(v * NE + e) * TPR + lir];
+              db[v][e] = reinterpret_cast<float2*>(cb_)[(v * NE + e) * TPR + lir];
+            }
           }
       }
     }
     if (group == 0) {
 #pragma unroll
       for (int v = 0; v < VPT; ++v) {
-        if (col[v] >= 0) {
-          store_params<EPV>(wg, col[v], dg[v]);
-          store_params<EPV>(wb, col[v], db[v]);
+        if (EXACT || v < nvalid) {
+          store_param_lanes<EPV>(wg, static_cast<int64_t>(vec0 + v * VSTRIDE) * EPV, dg[v]);
+          store_param_lanes<EPV>(wb, static_cast<int64_t>(vec0 + v * VSTRIDE) * EPV, db[v]);
         }
       }
     }
@@ -381,16 +492,17 @@ inline int resident_units(Kernel kernel, int block, int cs) {
   return clusters;
 }
 
-template <typename T, int EPV, int VPT, int TPR, int CS, bool ROW_AFFINE, bool BWD>
-inline cudaError_t launch_rows_one(const RowsArgs& a, cudaStream_t stream, bool dry_run,
-                                   RowsPlan* plan) {
+template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, bool PF,
+          bool EXACT, bool ROW_AFFINE, bool BWD>
+inline cudaError_t launch_rows_exact(const RowsArgs& a, cudaStream_t stream, bool dry_run,
+                                     RowsPlan* plan) {
   constexpr int BLOCK = RowBlock<TPR>::kBlock;
   constexpr int RPC = RowBlock<TPR>::kRowsPerCta;
   void (*kernel)(const RowsArgs);
   if constexpr (BWD) {
-    kernel = rows_bwd_kernel<T, EPV, VPT, TPR, CS, ROW_AFFINE>;
+    kernel = rows_bwd_kernel<T, EPV, TPR, VPT, CS, RB, PR, MINB, PF, EXACT, ROW_AFFINE>;
   } else {
-    kernel = rows_fwd_kernel<T, EPV, VPT, TPR, CS, ROW_AFFINE>;
+    kernel = rows_fwd_kernel<T, EPV, TPR, VPT, CS, RB, PR, MINB, PF, EXACT, ROW_AFFINE>;
   }
   // Cached per process: every device this library runs on is the same part.
   static std::atomic<int> cached_units{0};
@@ -404,14 +516,16 @@ inline cudaError_t launch_rows_one(const RowsArgs& a, cudaStream_t stream, bool 
     units = resident_units(kernel, BLOCK, CS);
     cached_units.store(units, std::memory_order_relaxed);
   }
-  const int64_t need = (a.N + RPC - 1) / RPC;
-  const int64_t use = need < units ? need : units;
+  const int64_t need = (a.N + RPC * RB - 1) / (RPC * RB);
+  int64_t use = need < units ? need : units;
+  if (!BWD && getenv("NVN_ONESHOT") != nullptr && need < 0x7fffffff / CS) use = need;
   plan->grid = static_cast<int>(use) * CS;
   plan->block = BLOCK;
   plan->cluster = CS;
   plan->tpr = TPR;
   plan->vpt = VPT;
   plan->epv = EPV;
+  plan->rb = RB;
   plan->partial_rows = static_cast<int>(use);
   if (dry_run) return cudaSuccess;
 
@@ -433,21 +547,37 @@ inline cudaError_t launch_rows_one(const RowsArgs& a, cudaStream_t stream, bool 
   return cudaLaunchKernelEx(&cfg, kernel, a);
 }
 
+template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, bool PF,
+          bool ROW_AFFINE, bool BWD>
+inline cudaError_t launch_rows_one(const RowsArgs& a, cudaStream_t stream, bool dry_run,
+                                   RowsPlan* plan) {
+  // Rows that fill the shape exactly skip every per-vector bounds check.
+  if (a.D == static_cast<int64_t>(TPR) * VPT * CS * EPV)
+    return launch_rows_exact<T, EPV, TPR, VPT, CS, RB, PR, MINB, PF, true, ROW_AFFINE, BWD>(
+        a, stream, dry_run, plan);
+  return launch_rows_exact<T, EPV, TPR, VPT, CS, RB, PR, MINB, PF, false, ROW_AFFINE, BWD>(
+      a, stream, dry_run, plan);
+}
+
+// The LayerNorm backward kernels carry the dgamma / dbeta accumulators and use
+// their own shape table; everything else (LayerNorm forward, InstanceNorm
+// forward and backward) shares the light table.
 template <typename T, bool ROW_AFFINE, bool BWD>
 cudaError_t launch_rows_vec(int shape, const RowsArgs& a, cudaStream_t s, bool dry, RowsPlan* p) {
   constexpr int EPV = VecTraits<T>::kFull;
-#define X(I, TPR, VPT, CS) \
-  case I:                  \
-    return launch_rows_one<T, EPV, VPT, TPR, CS, ROW_AFFINE, BWD>(a, s, dry, p);
-  if constexpr (BWD) {
+#define X(I, TPR, VPT, CS, RB, PR, MINB, PF) \
+  case I:                                    \
+    return launch_rows_one<T, EPV, TPR, VPT, CS, RB, PR != 0, MINB, PF != 0, ROW_AFFINE, BWD>( \
+        a, s, dry, p);
+  if constexpr (BWD && !ROW_AFFINE) {
     switch (shape) {
-      NVN_ROW_SHAPES_BWD(X)
+      NVN_ROW_SHAPES_HEAVY(X)
       default:
         return cudaErrorInvalidValue;
     }
   } else {
     switch (shape) {
-      NVN_ROW_SHAPES_FWD(X)
+      NVN_ROW_SHAPES_LIGHT(X)
       default:
         return cudaErrorInvalidValue;
     }
@@ -459,9 +589,10 @@ template <typename T, bool ROW_AFFINE, bool BWD>
 cudaError_t launch_rows_scalar(int shape, const RowsArgs& a, cudaStream_t s, bool dry,
                                RowsPlan* p) {
   switch (shape) {
-#define X(I, TPR, VPT, CS) \
-  case I:                  \
-    return launch_rows_one<T, 1, VPT, TPR, CS, ROW_AFFINE, BWD>(a, s, dry, p);
+#define X(I, TPR, VPT, CS, RB, PR, MINB, PF) \
+  case I:                                    \
+    return launch_rows_one<T, 1, TPR, VPT, CS, RB, PR != 0, MINB, PF != 0, ROW_AFFINE, BWD>( \
+        a, s, dry, p);
     NVN_ROW_SHAPES_SCALAR(X)
 #undef X
     default:
