@@ -158,6 +158,27 @@ NVN_API int nvn_in_bwd(int dtype, const void* dy, const void* x, const float* ga
                        float* dbeta, void* workspace, size_t workspace_bytes,
                        void* stream);
 
+/* ---- LayerNorm backward without a caller-provided workspace ------------------
+ * Same computation and results as nvn_ln_bwd, for callers that cannot supply
+ * scratch memory: a plugin callback that receives only input and output
+ * pointers, a process whose device memory is entirely owned by another pool, or
+ * a loop in which cudaMalloc / cudaFree are not allowed.  The dgamma / dbeta
+ * partial rows go to a fixed array of NVN_NOALLOC_SCRATCH_BYTES that is part of
+ * the library image (every GPU that loads the library holds it until exit).
+ *   - Returns NVN_ERR_LIMIT when nvn_ln_bwd_workspace_bytes(dtype, N, D) exceeds
+ *     NVN_NOALLOC_SCRATCH_BYTES; nothing is launched in that case.
+ *   - Allocates nothing, on the host or the device.
+ *   - All calls on a device share the array: calls that may overlap on the GPU
+ *     race on it and must be ordered by the caller (one stream, or events).
+ *     No part of the array needs zeroing between calls.
+ *   - The first call on each device looks up the array's address; make it before
+ *     any stream capture on that device.
+ * This entry point has no counterpart in the reference. */
+#define NVN_NOALLOC_SCRATCH_BYTES (16u << 20)
+NVN_API int nvn_ln_bwd_noalloc(int dtype, const void* dy, const void* x, const float* gamma,
+                               const float* mean, const float* inv_std, int64_t N, int64_t D,
+                               void* dx, float* dgamma, float* dbeta, void* stream);
+
 /* ---- introspection (for tests, benchmarks and profiles) ---------------------
  * Writes a short description of the kernel variant the dispatcher would pick,
  * e.g. "rows tpr=256 vpt=2 cluster=1 epv=8 grid=592".  op: 0 = ln_fwd,
