@@ -87,6 +87,13 @@ __device__ __forceinline__ Pack<T, EPV> load_stream(const T* base, int64_t elem_
   }
 }
 
+// Ordinary cached load for data that a following kernel reads again and should
+// find in L2 (phase 1 of the two-phase paths).
+template <typename T, int EPV>
+__device__ __forceinline__ Pack<T, EPV> load_keep(const T* p) {
+  return *reinterpret_cast<const Pack<T, EPV>*>(p);
+}
+
 template <typename T, int EPV>
 __device__ __forceinline__ void store_stream(T* base, int64_t elem_off, const Pack<T, EPV>& v) {
   using P = Pack<T, EPV>;

@@ -238,7 +238,7 @@ int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, 
   p->scalar = !(vec_ok && C % V == 0);
   const int epv = p->scalar ? 1 : V;
   if (N > 65535) return NVN_ERR_UNSUPPORTED;
-  p->s2 = s2_plan(N, C, D, epv);
+  p->s2 = s2_plan(dtype, bwd, N, C, D, epv);
   if (p->s2.ctiles > 65535) return NVN_ERR_UNSUPPORTED;
   size_t off = 0;
   p->off_part = off;
@@ -515,10 +515,9 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
     int st = plan_nlc(dtype, bwd, N, C, D, true, &p);
     if (st != NVN_OK) return st;
     snprintf(out, out_bytes,
-             "nlc two-phase epv=%d cvt=%d lanes=%d ctiles=%d chunk=%lld nchunks=%d grid=%lld",
+             "nlc two-phase epv=%d cvt=%d lanes=%d ctiles=%d chunk=%lld nchunks=%d group=%d",
              p.scalar ? 1 : full_epv(dtype), p.s2.cvt, p.s2.lanes, p.s2.ctiles,
-             static_cast<long long>(p.s2.chunk), p.s2.nchunks,
-             static_cast<long long>(p.s2.nchunks) * p.s2.ctiles * N);
+             static_cast<long long>(p.s2.chunk), p.s2.nchunks, p.s2.group);
     return NVN_OK;
   }
   const int64_t rows = is_in ? N * C : N;

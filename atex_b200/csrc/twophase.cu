@@ -384,47 +384,118 @@ struct S2Geom {
   int nchunks;
   int cvt;    // channel vectors per tile (<= 256)
   int lanes;  // voxel lanes per CTA = 256 / cvt
+  int64_t n0;   // first batch item of this launch (grid.z counts items from here)
+  int reverse;  // phase 2: visit items and chunks last-to-first, so that what phase 1
+                // read most recently (and is most likely still in L2) is re-read first
 };
 
+__device__ __forceinline__ int64_t s2_item(const S2Geom& gm) {
+  return gm.n0 + (gm.reverse ? (gridDim.z - 1 - blockIdx.z) : blockIdx.z);
+}
+__device__ __forceinline__ int s2_chunk(const S2Geom& gm) {
+  return gm.reverse ? (gm.nchunks - 1 - static_cast<int>(blockIdx.x)) : static_cast<int>(blockIdx.x);
+}
+
+// a - b on math lanes
+template <typename M>
+__device__ __forceinline__ typename M::E lane_sub(typename M::E a, typename M::E b) {
+  return M::fma(b, M::bcast(-1.f), a);
+}
+
+// Per-thread geometry of the S2 kernels: which channel vector and which voxels
+// (d0 + ty, d0 + ty + lanes, ...) of the chunk this thread owns.
+struct S2Thread {
+  int tx, ty;
+  int64_t cv;      // channel-vector index
+  bool active;
+  int64_t count;   // voxels of this thread inside the chunk
+  int64_t first;   // element offset of its first vector
+  int64_t step;    // element distance between its consecutive voxels
+};
+
+template <int EPV>
+__device__ __forceinline__ S2Thread s2_thread(const S2Geom& gm) {
+  S2Thread t;
+  t.tx = threadIdx.x % gm.cvt;
+  t.ty = threadIdx.x / gm.cvt;
+  t.cv = static_cast<int64_t>(blockIdx.y) * gm.cvt + t.tx;
+  const int64_t n = s2_item(gm);
+  const int64_t d0 = static_cast<int64_t>(s2_chunk(gm)) * gm.chunk;
+  const int64_t d1 = d0 + gm.chunk < gm.D ? d0 + gm.chunk : gm.D;
+  t.active = t.ty < gm.lanes && t.cv * EPV < gm.C && d0 + t.ty < d1;
+  t.count = t.active ? (d1 - d0 - t.ty + gm.lanes - 1) / gm.lanes : 0;
+  t.first = ((n * gm.D) + d0 + t.ty) * gm.C + t.cv * EPV;
+  t.step = static_cast<int64_t>(gm.lanes) * gm.C;
+  return t;
+}
+
 // ws layout for phase-1 partials: [n][chunk][k][C], k = 0..K-1
+//
+// Forward statistics.  Every thread walks its voxels in batches of kUnroll: the
+// batch is reduced exactly (mean, then centred squares, on fp32x2 lanes) and
+// folded into the running (mean, M2, n) with Chan's update, whose two weights are
+// shared by all channels of the thread.  Leftover voxels use the per-element
+// Welford update.
 template <typename T, int EPV>
 __global__ void __launch_bounds__(kBlock)
     s2_stats_fwd_kernel(const T* __restrict__ x, const S2Geom gm, float* __restrict__ ws) {
-  extern __shared__ float dyn[];  // [lanes][cvt*EPV] x (mean, m2) ; counts in cnt[]
-  const int tx = threadIdx.x % gm.cvt;
-  const int ty = threadIdx.x / gm.cvt;
-  const int64_t n = blockIdx.z;
-  const int64_t cv = static_cast<int64_t>(blockIdx.y) * gm.cvt + tx;
-  const bool active = ty < gm.lanes && cv * EPV < gm.C;
-  const int chunk_id = blockIdx.x;
-  const int64_t d0 = static_cast<int64_t>(chunk_id) * gm.chunk;
-  const int64_t d1 = d0 + gm.chunk < gm.D ? d0 + gm.chunk : gm.D;
+  using M = typename MathSel<EPV>::M;
+  using E = typename M::E;
+  constexpr int NE = MathSel<EPV>::NE;
+  extern __shared__ float dyn[];  // [lanes][cvt*EPV] x (mean, m2) ; counts [lanes][cvt]
+  const S2Thread th = s2_thread<EPV>(gm);
+  const int tx = th.tx, ty = th.ty;
+  const int64_t n = s2_item(gm);
+  const int chunk_id = s2_chunk(gm);
 
-  float mean[EPV], m2[EPV];
+  E mean[NE], m2[NE];
 #pragma unroll
-  for (int e = 0; e < EPV; ++e) mean[e] = m2[e] = 0.f;
+  for (int e = 0; e < NE; ++e) mean[e] = m2[e] = M::bcast(0.f);
   float cnt = 0.f;
-  if (active) {
-    const T* base = x + (n * gm.D) * gm.C + cv * EPV;
-    for (int64_t d = d0 + ty; d < d1; d += static_cast<int64_t>(kUnroll) * gm.lanes) {
-      Pack<T, EPV> p[kUnroll];
+  if (th.active) {
+    const T* p = x + th.first;
+    int64_t i = 0;
+    for (; i + kUnroll <= th.count; i += kUnroll) {
+      Pack<T, EPV> pk[kUnroll];
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u)
-        if (d + static_cast<int64_t>(u) * gm.lanes < d1)
-          p[u] = load_stream<T, EPV>(base, (d + static_cast<int64_t>(u) * gm.lanes) * gm.C);
+      for (int u = 0; u < kUnroll; ++u) pk[u] = load_keep<T, EPV>(p + u * th.step);
+      p += kUnroll * th.step;
+      E v[kUnroll][NE];
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        if (d + static_cast<int64_t>(u) * gm.lanes < d1) {
-          cnt += 1.f;
-          const float inv = 1.0f / cnt;
+      for (int u = 0; u < kUnroll; ++u) unpack<T, EPV>(pk[u], v[u]);
+      const float nn = cnt + static_cast<float>(kUnroll);
+      const float w1 = __fdividef(static_cast<float>(kUnroll), nn);
+      const E w1v = M::bcast(w1), w2v = M::bcast(cnt * w1);
 #pragma unroll
-          for (int e = 0; e < EPV; ++e) {
-            const float v = Cvt<T>::to_f32(p[u].v[e]);
-            const float dl = v - mean[e];
-            mean[e] = fmaf(dl, inv, mean[e]);
-            m2[e] = fmaf(dl, v - mean[e], m2[e]);
-          }
+      for (int e = 0; e < NE; ++e) {
+        E sum = v[0][e];
+#pragma unroll
+        for (int u = 1; u < kUnroll; ++u) sum = M::add(sum, v[u][e]);
+        const E bm = M::mul(sum, M::bcast(1.0f / kUnroll));
+        E bq = M::bcast(0.f);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const E d = lane_sub<M>(v[u][e], bm);
+          bq = M::fma(d, d, bq);
         }
+        const E delta = lane_sub<M>(bm, mean[e]);
+        mean[e] = M::fma(delta, w1v, mean[e]);
+        m2[e] = M::fma(M::mul(delta, delta), w2v, M::add(m2[e], bq));
+      }
+      cnt = nn;
+    }
+    for (; i < th.count; ++i) {
+      const Pack<T, EPV> pk = load_keep<T, EPV>(p);
+      p += th.step;
+      E v[NE];
+      unpack<T, EPV>(pk, v);
+      cnt += 1.f;
+      const E inv = M::bcast(1.0f / cnt);
+#pragma unroll
+      for (int e = 0; e < NE; ++e) {
+        const E dl = lane_sub<M>(v[e], mean[e]);
+        mean[e] = M::fma(dl, inv, mean[e]);
+        m2[e] = M::fma(dl, lane_sub<M>(v[e], mean[e]), m2[e]);
       }
     }
   }
@@ -434,22 +505,35 @@ __global__ void __launch_bounds__(kBlock)
   float* s_m2 = dyn + gm.lanes * width;
   float* s_cnt = dyn + 2 * gm.lanes * width;  // [lanes][cvt]
   if (ty < gm.lanes) {
+    float fm[EPV], fq[EPV];
+    if constexpr (EPV == 1) {
+      fm[0] = mean[0];
+      fq[0] = m2[0];
+    } else {
+#pragma unroll
+      for (int e = 0; e < NE; ++e) {
+        fm[2 * e] = mean[e].x;
+        fm[2 * e + 1] = mean[e].y;
+        fq[2 * e] = m2[e].x;
+        fq[2 * e + 1] = m2[e].y;
+      }
+    }
 #pragma unroll
     for (int e = 0; e < EPV; ++e) {
-      s_mean[ty * width + tx * EPV + e] = mean[e];
-      s_m2[ty * width + tx * EPV + e] = m2[e];
+      s_mean[ty * width + tx * EPV + e] = fm[e];
+      s_m2[ty * width + tx * EPV + e] = fq[e];
     }
     s_cnt[ty * gm.cvt + tx] = cnt;
   }
   __syncthreads();
   int span = 1;
   while (span < gm.lanes) span <<= 1;
-  for (int s = span >> 1; s > 0; s >>= 1) {
-    if (ty < s && ty + s < gm.lanes) {
-      const float na = s_cnt[ty * gm.cvt + tx], nb = s_cnt[(ty + s) * gm.cvt + tx];
+  for (int sft = span >> 1; sft > 0; sft >>= 1) {
+    if (ty < sft && ty + sft < gm.lanes) {
+      const float na = s_cnt[ty * gm.cvt + tx], nb = s_cnt[(ty + sft) * gm.cvt + tx];
 #pragma unroll
       for (int e = 0; e < EPV; ++e) {
-        const int ia = ty * width + tx * EPV + e, ib = (ty + s) * width + tx * EPV + e;
+        const int ia = ty * width + tx * EPV + e, ib = (ty + sft) * width + tx * EPV + e;
         WF a = {s_mean[ia], s_m2[ia], na};
         WF b = {s_mean[ib], s_m2[ib], nb};
         const WF r = wf_merge(a, b);
@@ -460,8 +544,8 @@ __global__ void __launch_bounds__(kBlock)
     }
     __syncthreads();
   }
-  if (ty == 0 && cv * EPV < gm.C) {
-    float* o = ws + ((n * gm.nchunks + chunk_id) * 3) * gm.C + cv * EPV;
+  if (ty == 0 && th.cv * EPV < gm.C) {
+    float* o = ws + ((n * gm.nchunks + chunk_id) * 3) * gm.C + th.cv * EPV;
 #pragma unroll
     for (int e = 0; e < EPV; ++e) {
       o[e] = s_mean[tx * EPV + e];
@@ -471,20 +555,35 @@ __global__ void __launch_bounds__(kBlock)
   }
 }
 
-__global__ void s2_finalize_fwd_kernel(const float* __restrict__ ws, int64_t N, int64_t C,
-                                       int nchunks, float eps, float* __restrict__ mean,
-                                       float* __restrict__ ivar) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= N * C) return;
+// One warp per (n, c): lane l merges chunks l, l+32, ... in increasing order, then
+// the 32 lane results are merged by a butterfly whose pairing is fixed.
+__global__ void s2_finalize_fwd_kernel(const float* __restrict__ ws, int64_t n0, int64_t items,
+                                       int64_t C, int nchunks, float eps,
+                                       float* __restrict__ mean, float* __restrict__ ivar) {
+  const int lane = threadIdx.x & 31;
+  const int64_t local = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (local >= items * C) return;  // whole warps leave together
+  const int64_t i = n0 * C + local;
   const int64_t n = i / C, c = i - n * C;
   WF t = {0.f, 0.f, 0.f};
-  for (int k = 0; k < nchunks; ++k) {
+  for (int k = lane; k < nchunks; k += 32) {
     const float* p = ws + ((n * nchunks + k) * 3) * C + c;
     WF b = {p[0], p[C], p[2 * C]};
     t = wf_merge(t, b);
   }
-  mean[i] = t.mean;
-  ivar[i] = 1.0f / sqrtf(t.m2 / t.n + eps);
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    WF o;
+    o.mean = __shfl_xor_sync(0xffffffffu, t.mean, off);
+    o.m2 = __shfl_xor_sync(0xffffffffu, t.m2, off);
+    o.n = __shfl_xor_sync(0xffffffffu, t.n, off);
+    const bool low = (lane & off) == 0;
+    t = low ? wf_merge(t, o) : wf_merge(o, t);
+  }
+  if (lane == 0) {
+    mean[i] = t.mean;
+    ivar[i] = 1.0f / sqrtf(t.m2 / t.n + eps);
+  }
 }
 
 template <typename T, int EPV>
@@ -494,10 +593,10 @@ __global__ void __launch_bounds__(kBlock)
                         const float* __restrict__ ivar, const S2Geom gm, T* y) {
   const int tx = threadIdx.x % gm.cvt;
   const int ty = threadIdx.x / gm.cvt;
-  const int64_t n = blockIdx.z;
+  const int64_t n = s2_item(gm);
   const int64_t cv = static_cast<int64_t>(blockIdx.y) * gm.cvt + tx;
   if (!(ty < gm.lanes && cv * EPV < gm.C)) return;
-  const int64_t d0 = static_cast<int64_t>(blockIdx.x) * gm.chunk;
+  const int64_t d0 = static_cast<int64_t>(s2_chunk(gm)) * gm.chunk;
   const int64_t d1 = d0 + gm.chunk < gm.D ? d0 + gm.chunk : gm.D;
   float mu[EPV], sc[EPV], sh[EPV];
 #pragma unroll
@@ -535,41 +634,53 @@ __global__ void __launch_bounds__(kBlock)
     s2_stats_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                         const float* __restrict__ mean, const S2Geom gm,
                         float* __restrict__ ws) {
+  using M = typename MathSel<EPV>::M;
+  using E = typename M::E;
+  constexpr int NE = MathSel<EPV>::NE;
   extern __shared__ float dyn[];  // [2][lanes][cvt*EPV]
-  const int tx = threadIdx.x % gm.cvt;
-  const int ty = threadIdx.x / gm.cvt;
-  const int64_t n = blockIdx.z;
-  const int64_t cv = static_cast<int64_t>(blockIdx.y) * gm.cvt + tx;
-  const bool active = ty < gm.lanes && cv * EPV < gm.C;
-  const int chunk_id = blockIdx.x;
-  const int64_t d0 = static_cast<int64_t>(chunk_id) * gm.chunk;
-  const int64_t d1 = d0 + gm.chunk < gm.D ? d0 + gm.chunk : gm.D;
-  float s0[EPV], s1[EPV], mu[EPV];
+  const S2Thread th = s2_thread<EPV>(gm);
+  const int tx = th.tx, ty = th.ty;
+  const int64_t n = s2_item(gm);
+  const int chunk_id = s2_chunk(gm);
+  E s0[NE], s1[NE];
 #pragma unroll
-  for (int e = 0; e < EPV; ++e) s0[e] = s1[e] = mu[e] = 0.f;
-  if (active) {
+  for (int e = 0; e < NE; ++e) s0[e] = s1[e] = M::bcast(0.f);
+  if (th.active) {
+    E nmu[NE];
+    {
+      float t[EPV];
 #pragma unroll
-    for (int e = 0; e < EPV; ++e) mu[e] = mean[n * gm.C + cv * EPV + e];
-    const T* xb = x + (n * gm.D) * gm.C + cv * EPV;
-    const T* db = dy + (n * gm.D) * gm.C + cv * EPV;
-    for (int64_t d = d0 + ty; d < d1; d += static_cast<int64_t>(kUnroll) * gm.lanes) {
-      Pack<T, EPV> px[kUnroll], pd[kUnroll];
+      for (int e = 0; e < EPV; ++e) t[e] = -mean[n * gm.C + th.cv * EPV + e];
+      if constexpr (EPV == 1) {
+        nmu[0] = t[0];
+      } else {
+#pragma unroll
+        for (int e = 0; e < NE; ++e) nmu[e] = make_float2(t[2 * e], t[2 * e + 1]);
+      }
+    }
+    const T* px = x + th.first;
+    const T* pd = dy + th.first;
+    for (int64_t i = 0; i < th.count; i += kUnroll) {
+      Pack<T, EPV> kx[kUnroll], kd[kUnroll];
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
-        const int64_t dd = d + static_cast<int64_t>(u) * gm.lanes;
-        if (dd < d1) {
-          px[u] = load_stream<T, EPV>(xb, dd * gm.C);
-          pd[u] = load_stream<T, EPV>(db, dd * gm.C);
+        if (i + u < th.count) {
+          kx[u] = load_keep<T, EPV>(px + u * th.step);
+          kd[u] = load_keep<T, EPV>(pd + u * th.step);
         }
       }
+      px += kUnroll * th.step;
+      pd += kUnroll * th.step;
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
-        if (d + static_cast<int64_t>(u) * gm.lanes < d1) {
+        if (i + u < th.count) {
+          E vx[NE], vd[NE];
+          unpack<T, EPV>(kx[u], vx);
+          unpack<T, EPV>(kd[u], vd);
 #pragma unroll
-          for (int e = 0; e < EPV; ++e) {
-            const float dv = Cvt<T>::to_f32(pd[u].v[e]);
-            s0[e] += dv;
-            s1[e] = fmaf(dv, Cvt<T>::to_f32(px[u].v[e]) - mu[e], s1[e]);
+          for (int e = 0; e < NE; ++e) {
+            s0[e] = M::add(s0[e], vd[e]);
+            s1[e] = M::fma(vd[e], M::add(vx[e], nmu[e]), s1[e]);
           }
         }
       }
@@ -579,28 +690,41 @@ __global__ void __launch_bounds__(kBlock)
   float* a0 = dyn;
   float* a1 = dyn + gm.lanes * width;
   if (ty < gm.lanes) {
+    float f0[EPV], f1[EPV];
+    if constexpr (EPV == 1) {
+      f0[0] = s0[0];
+      f1[0] = s1[0];
+    } else {
+#pragma unroll
+      for (int e = 0; e < NE; ++e) {
+        f0[2 * e] = s0[e].x;
+        f0[2 * e + 1] = s0[e].y;
+        f1[2 * e] = s1[e].x;
+        f1[2 * e + 1] = s1[e].y;
+      }
+    }
 #pragma unroll
     for (int e = 0; e < EPV; ++e) {
-      a0[ty * width + tx * EPV + e] = s0[e];
-      a1[ty * width + tx * EPV + e] = s1[e];
+      a0[ty * width + tx * EPV + e] = f0[e];
+      a1[ty * width + tx * EPV + e] = f1[e];
     }
   }
   __syncthreads();
   int span = 1;
   while (span < gm.lanes) span <<= 1;
-  for (int s = span >> 1; s > 0; s >>= 1) {
-    if (ty < s && ty + s < gm.lanes) {
+  for (int sft = span >> 1; sft > 0; sft >>= 1) {
+    if (ty < sft && ty + sft < gm.lanes) {
 #pragma unroll
       for (int e = 0; e < EPV; ++e) {
-        const int ia = ty * width + tx * EPV + e, ib = (ty + s) * width + tx * EPV + e;
+        const int ia = ty * width + tx * EPV + e, ib = (ty + sft) * width + tx * EPV + e;
         a0[ia] += a0[ib];
         a1[ia] += a1[ib];
       }
     }
     __syncthreads();
   }
-  if (ty == 0 && cv * EPV < gm.C) {
-    float* o = ws + ((n * gm.nchunks + chunk_id) * 2) * gm.C + cv * EPV;
+  if (ty == 0 && th.cv * EPV < gm.C) {
+    float* o = ws + ((n * gm.nchunks + chunk_id) * 2) * gm.C + th.cv * EPV;
 #pragma unroll
     for (int e = 0; e < EPV; ++e) {
       o[e] = a0[tx * EPV + e];
@@ -613,26 +737,35 @@ __global__ void __launch_bounds__(kBlock)
 // part: [n][2][C] = (dgamma_nc, dbeta_nc)
 __global__ void s2_finalize_bwd_kernel(const float* __restrict__ ws,
                                        const float* __restrict__ gamma,
-                                       const float* __restrict__ ivar, int64_t N, int64_t C,
-                                       int64_t D, int nchunks, float* __restrict__ coef,
-                                       float* __restrict__ part) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= N * C) return;
+                                       const float* __restrict__ ivar, int64_t n0,
+                                       int64_t items, int64_t C, int64_t D, int nchunks,
+                                       float* __restrict__ coef, float* __restrict__ part) {
+  const int lane = threadIdx.x & 31;
+  const int64_t local = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (local >= items * C) return;  // whole warps leave together
+  const int64_t i = n0 * C + local;
   const int64_t n = i / C, c = i - n * C;
   float r0 = 0.f, r1 = 0.f;
-  for (int k = 0; k < nchunks; ++k) {
+  for (int k = lane; k < nchunks; k += 32) {
     const float* p = ws + ((n * nchunks + k) * 2) * C + c;
     r0 += p[0];
     r1 += p[C];
   }
-  const float iv = ivar[i];
-  const float inv_D = 1.0f / static_cast<float>(D);
-  const float dgam = r1 * iv;  // sum dy * xhat
-  coef[(n * 3 + 0) * C + c] = gamma[c] * iv;
-  coef[(n * 3 + 1) * C + c] = r0 * inv_D;
-  coef[(n * 3 + 2) * C + c] = dgam * inv_D * iv;  // multiplies (x - mean)
-  part[(n * 2 + 0) * C + c] = dgam;
-  part[(n * 2 + 1) * C + c] = r0;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    r0 += __shfl_xor_sync(0xffffffffu, r0, off);
+    r1 += __shfl_xor_sync(0xffffffffu, r1, off);
+  }
+  if (lane == 0) {
+    const float iv = ivar[i];
+    const float inv_D = 1.0f / static_cast<float>(D);
+    const float dgam = r1 * iv;  // sum dy * xhat
+    coef[(n * 3 + 0) * C + c] = gamma[c] * iv;
+    coef[(n * 3 + 1) * C + c] = r0 * inv_D;
+    coef[(n * 3 + 2) * C + c] = dgam * inv_D * iv;  // multiplies (x - mean)
+    part[(n * 2 + 0) * C + c] = dgam;
+    part[(n * 2 + 1) * C + c] = r0;
+  }
 }
 
 template <typename T, int EPV>
@@ -642,10 +775,10 @@ __global__ void __launch_bounds__(kBlock)
                         const S2Geom gm, T* __restrict__ dx) {
   const int tx = threadIdx.x % gm.cvt;
   const int ty = threadIdx.x / gm.cvt;
-  const int64_t n = blockIdx.z;
+  const int64_t n = s2_item(gm);
   const int64_t cv = static_cast<int64_t>(blockIdx.y) * gm.cvt + tx;
   if (!(ty < gm.lanes && cv * EPV < gm.C)) return;
-  const int64_t d0 = static_cast<int64_t>(blockIdx.x) * gm.chunk;
+  const int64_t d0 = static_cast<int64_t>(s2_chunk(gm)) * gm.chunk;
   const int64_t d1 = d0 + gm.chunk < gm.D ? d0 + gm.chunk : gm.D;
   float mu[EPV], sc[EPV], m0[EPV], m1[EPV];
 #pragma unroll
@@ -810,16 +943,24 @@ cudaError_t r2_launch(int dtype, bool bwd, bool scalar, const R2Args& a, const R
 }
 
 // ---- S2 planning -----------------------------------------------------------
-S2Plan s2_plan(int64_t N, int64_t C, int64_t D, int epv) {
+S2Plan s2_plan(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, int epv) {
   S2Plan p = {};
   const int sms = device_sm_count();
   const int64_t CV = C / epv;
   p.cvt = static_cast<int>(CV < kBlock ? CV : kBlock);
   p.lanes = kBlock / p.cvt;
   p.ctiles = static_cast<int>(ceil_div(CV, p.cvt));
+  // All items go into one launch group.  (Splitting the batch into L2-sized groups so that
+  // phase 2 re-reads a group straight from L2 was measured on B200 with 134 MB items and lost
+  // more to small launches than it gained; the launch code still supports groups.)  Phase 2
+  // walks items and chunks in reverse, which keeps the tail of phase 1 an L2 hit.
+  (void)dtype;
+  (void)bwd;
+  const int64_t group = N;
+  p.group = static_cast<int>(group);
   // voxels one CTA sweep covers
   const int64_t sweep = static_cast<int64_t>(p.lanes) * kUnroll;
-  int64_t want = ceil_div(static_cast<int64_t>(sms) * 8, N * p.ctiles);
+  int64_t want = ceil_div(static_cast<int64_t>(sms) * 8, group * p.ctiles);
   if (want < 1) want = 1;
   int64_t chunk = round_up(ceil_div(D, want), sweep);
   // keep at least 8 sweeps per chunk so the per-chunk merge stays negligible
@@ -841,29 +982,38 @@ static cudaError_t s2_t(bool bwd, const S2Args& a, const S2Plan& p, cudaStream_t
   gm.nchunks = p.nchunks;
   gm.cvt = p.cvt;
   gm.lanes = p.lanes;
-  const dim3 grid(static_cast<unsigned>(p.nchunks), static_cast<unsigned>(p.ctiles),
-                  static_cast<unsigned>(a.N));
-  const unsigned fin_blocks = static_cast<unsigned>(ceil_div(a.N * a.C, 128));
   const T* x = static_cast<const T*>(a.x);
-  if (!bwd) {
-    s2_stats_fwd_kernel<T, EPV><<<grid, kBlock, p.smem_fwd, s>>>(x, gm, a.ws_part);
-    NVN_LAUNCHED();
-    s2_finalize_fwd_kernel<<<fin_blocks, 128, 0, s>>>(a.ws_part, a.N, a.C, p.nchunks, a.eps,
-                                                      a.mean, a.ivar);
-    NVN_LAUNCHED();
-    s2_apply_fwd_kernel<T, EPV><<<grid, kBlock, 0, s>>>(x, a.gamma, a.beta, a.mean, a.ivar, gm,
-                                                        static_cast<T*>(a.out));
-    NVN_LAUNCHED();
-  } else {
-    const T* dy = static_cast<const T*>(a.dy);
-    s2_stats_bwd_kernel<T, EPV><<<grid, kBlock, p.smem_bwd, s>>>(dy, x, a.mean, gm, a.ws_part);
-    NVN_LAUNCHED();
-    s2_finalize_bwd_kernel<<<fin_blocks, 128, 0, s>>>(a.ws_part, a.gamma, a.ivar, a.N, a.C, a.D,
-                                                      p.nchunks, a.ws_coef, a.ws_colpart);
-    NVN_LAUNCHED();
-    s2_apply_bwd_kernel<T, EPV><<<grid, kBlock, 0, s>>>(dy, x, a.mean, a.ws_coef, gm,
-                                                        static_cast<T*>(a.out));
-    NVN_LAUNCHED();
+  const T* dy = static_cast<const T*>(a.dy);
+  for (int64_t n0 = 0; n0 < a.N; n0 += p.group) {
+    const int64_t items = n0 + p.group <= a.N ? p.group : a.N - n0;
+    const dim3 grid(static_cast<unsigned>(p.nchunks), static_cast<unsigned>(p.ctiles),
+                    static_cast<unsigned>(items));
+    // finalize kernels use one warp per (n, c): 4 per 128-thread block
+    const unsigned fin_blocks = static_cast<unsigned>(ceil_div(items * a.C, 4));
+    gm.n0 = n0;
+    gm.reverse = 0;
+    S2Geom back = gm;
+    back.reverse = 1;
+    if (!bwd) {
+      s2_stats_fwd_kernel<T, EPV><<<grid, kBlock, p.smem_fwd, s>>>(x, gm, a.ws_part);
+      NVN_LAUNCHED();
+      s2_finalize_fwd_kernel<<<fin_blocks, 128, 0, s>>>(a.ws_part, n0, items, a.C, p.nchunks,
+                                                        a.eps, a.mean, a.ivar);
+      NVN_LAUNCHED();
+      s2_apply_fwd_kernel<T, EPV><<<grid, kBlock, 0, s>>>(x, a.gamma, a.beta, a.mean, a.ivar,
+                                                          back, static_cast<T*>(a.out));
+      NVN_LAUNCHED();
+    } else {
+      s2_stats_bwd_kernel<T, EPV><<<grid, kBlock, p.smem_bwd, s>>>(dy, x, a.mean, gm, a.ws_part);
+      NVN_LAUNCHED();
+      s2_finalize_bwd_kernel<<<fin_blocks, 128, 0, s>>>(a.ws_part, a.gamma, a.ivar, n0, items,
+                                                        a.C, a.D, p.nchunks, a.ws_coef,
+                                                        a.ws_colpart);
+      NVN_LAUNCHED();
+      s2_apply_bwd_kernel<T, EPV><<<grid, kBlock, 0, s>>>(dy, x, a.mean, a.ws_coef, back,
+                                                          static_cast<T*>(a.out));
+      NVN_LAUNCHED();
+    }
   }
   return cudaSuccess;
 }

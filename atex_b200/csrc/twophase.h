@@ -45,6 +45,7 @@ struct S2Plan {
   int cvt;     // channel vectors per CTA tile
   int lanes;   // voxel lanes per CTA
   int ctiles;  // channel tiles
+  int group;   // batch items per launch group
   size_t smem_fwd;
   size_t smem_bwd;
 };
@@ -66,7 +67,7 @@ struct S2Args {
   float eps;
 };
 
-S2Plan s2_plan(int64_t N, int64_t C, int64_t D, int epv);
+S2Plan s2_plan(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, int epv);
 cudaError_t s2_launch(int dtype, bool bwd, bool scalar, const S2Args& a, const S2Plan& p,
                       cudaStream_t s);
 

@@ -47,6 +47,9 @@ def parse_args():
     p.add_argument("--workload", default="c2")
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    p.add_argument("--batch", type=int, default=0,
+                   help="override the per-GPU batch extent (rows / batch items); used for small "
+                        "profiler captures, not for reported numbers")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     return p.parse_args()
@@ -114,6 +117,8 @@ def run_reference_arm(args, rank, world):
     from oracle import oracle
     oracle.build()
     w = T.WORKLOADS[args.workload]
+    if args.batch:
+        w = T.scaled(w, args.batch)
     n = cpu_sample(w)
     ws = T.scaled(w, n)
     x, dy = T.make_activations(ws)
@@ -241,6 +246,8 @@ def main():
     lib = _lib.load()
 
     w = T.WORKLOADS[args.workload]
+    if args.batch:
+        w = T.scaled(w, args.batch)
     if args.scaling == "weak":
         a, b = rank * w.N, (rank + 1) * w.N
         wl = w
