@@ -2,11 +2,13 @@
 //
 // Stage one (the backward kernels) leaves P partial rows of [2][F] floats in the
 // workspace: row p holds the dgamma contributions of one CTA / cluster / batch
-// item followed by its dbeta contributions.  This kernel sums the P rows per
-// column.  Thread (tx, ty) of a 32 x 32 CTA adds rows ty, ty+32, ... of column
-// blockIdx.x*32 + tx in increasing order; the 32 ty-partials are then added in
+// item / row slice followed by its dbeta contributions.  This kernel sums the P
+// rows per column.  Thread (tx, ty) of a 32 x TY CTA adds rows ty, ty+TY, ... of
+// its columns in increasing order; the TY partial sums are then added in
 // increasing ty.  The order never depends on timing, so the result is
-// bit-identical from run to run.
+// bit-identical from run to run.  TY follows P (few partial rows: small CTAs and
+// many of them; many partial rows: 32 row lanes); when 2F is a multiple of 4 a
+// thread covers four adjacent columns with 128-bit loads.
 //
 // Replaces LayerNormGradBetaGammaTempToOut (atex/nv_norms/cc/kernels/
 // fused_layer_norm_op.cu:784-803) and ReduceNCtoC (fused_instance_norm_op.cu:442-457).
@@ -16,41 +18,72 @@ namespace nvn {
 
 namespace {
 constexpr int kTX = 32;
-constexpr int kTY = 32;
 
-__global__ void __launch_bounds__(kTX* kTY)
+template <int TY, int W>  // W columns per thread: 4 (float4) or 1
+__global__ void __launch_bounds__(kTX* TY)
     colreduce_kernel(const float* __restrict__ partials, int64_t P, int64_t F,
                      float* __restrict__ dgamma, float* __restrict__ dbeta) {
-  __shared__ float tile[kTY][kTX + 1];
+  __shared__ float tile[TY][kTX * W + 1];
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int64_t F2 = 2 * F;
-  const int64_t col = static_cast<int64_t>(blockIdx.x) * kTX + tx;
-  float s = 0.f;
-  if (col < F2) {
-    for (int64_t p = ty; p < P; p += kTY) s += partials[p * F2 + col];
-  }
-  tile[ty][tx] = s;
-  __syncthreads();
-  if (ty == 0 && col < F2) {
-    float t = 0.f;
+  const int64_t col = (static_cast<int64_t>(blockIdx.x) * kTX + tx) * W;
+  float s[W];
 #pragma unroll
-    for (int k = 0; k < kTY; ++k) t += tile[k][tx];
-    if (col < F) {
-      dgamma[col] = t;
-    } else {
-      dbeta[col - F] = t;
+  for (int w = 0; w < W; ++w) s[w] = 0.f;
+  if (col < F2) {
+    for (int64_t p = ty; p < P; p += TY) {
+      if constexpr (W == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(partials + p * F2 + col);
+        s[0] += v.x;
+        s[1] += v.y;
+        s[2] += v.z;
+        s[3] += v.w;
+      } else {
+        s[0] += partials[p * F2 + col];
+      }
     }
   }
+#pragma unroll
+  for (int w = 0; w < W; ++w) tile[ty][tx * W + w] = s[w];
+  __syncthreads();
+  if (ty == 0 && col < F2) {
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+      float t = 0.f;
+#pragma unroll
+      for (int k = 0; k < TY; ++k) t += tile[k][tx * W + w];
+      const int64_t c = col + w;
+      if (c < F) {
+        dgamma[c] = t;
+      } else {
+        dbeta[c - F] = t;
+      }
+    }
+  }
+}
+
+template <int TY, int W>
+cudaError_t launch(const float* partials, int64_t P, int64_t F, float* dgamma, float* dbeta,
+                   cudaStream_t s) {
+  const int64_t blocks = (2 * F + kTX * W - 1) / (kTX * W);
+  count_launch();
+  colreduce_kernel<TY, W><<<static_cast<unsigned>(blocks), dim3(kTX, TY), 0, s>>>(
+      partials, P, F, dgamma, dbeta);
+  return cudaGetLastError();
 }
 }  // namespace
 
 cudaError_t colreduce_launch(const float* partials, int64_t P, int64_t F, float* dgamma,
                              float* dbeta, cudaStream_t s) {
-  const int64_t blocks = (2 * F + kTX - 1) / kTX;
-  count_launch();
-  colreduce_kernel<<<static_cast<unsigned>(blocks), dim3(kTX, kTY), 0, s>>>(partials, P, F,
-                                                                           dgamma, dbeta);
-  return cudaGetLastError();
+  const bool vec = (2 * F) % 4 == 0 && (reinterpret_cast<uintptr_t>(partials) & 15) == 0;
+  if (vec) {
+    if (P <= 4) return launch<1, 4>(partials, P, F, dgamma, dbeta, s);
+    if (P <= 32) return launch<4, 4>(partials, P, F, dgamma, dbeta, s);
+    if (P <= 128 || 2 * F >= 32768) return launch<8, 4>(partials, P, F, dgamma, dbeta, s);
+    return launch<32, 4>(partials, P, F, dgamma, dbeta, s);
+  }
+  if (P <= 32) return launch<4, 1>(partials, P, F, dgamma, dbeta, s);
+  return launch<32, 1>(partials, P, F, dgamma, dbeta, s);
 }
 
 }  // namespace nvn

@@ -114,6 +114,14 @@ int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int
   const char* env = p->scalar ? nullptr : (bwd ? "NVN_FORCE_BWD_SHAPE" : "NVN_FORCE_FWD_SHAPE");
   p->shape = pick_shape(table, ntab, nvec, env);
   p->two_phase = p->shape < 0;
+  // Rows that need a cluster could also take the two-phase path (phase 2 then re-reads
+  // from L2 when the problem is small).  Measured on B200 for [256, 65536] fp16 the two are
+  // equal (70 us fwd+bwd), so the single-launch cluster kernel stays the default;
+  // NVN_WIDE_ROWS=twophase switches for experiments.
+  if (!p->two_phase && table[p->shape].cs > 1) {
+    const char* v = getenv("NVN_WIDE_ROWS");
+    if (v != nullptr && v[0] == 't') p->two_phase = true;
+  }
   size_t off = 0;
   if (!p->two_phase) {
     RowsArgs a = {};

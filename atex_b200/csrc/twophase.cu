@@ -113,36 +113,71 @@ __device__ __forceinline__ void sum_block_reduce(float (&v)[NV], float* smem /*[
   __syncthreads();
 }
 
+// a - b on math lanes
+template <typename M>
+__device__ __forceinline__ typename M::E lane_sub(typename M::E a, typename M::E b) {
+  return M::fma(b, M::bcast(-1.f), a);
+}
+
 // ===========================================================================
 // Family R2: [rows, D], D contiguous
+//
+// grid = (rows, chunks of D).  Phase 1 reads with ordinary cached loads so that,
+// when the whole problem is smaller than L2, phase 2 re-reads it from there.
 // ===========================================================================
 
-// ws_wf: [rows][nchunks][3] = (mean, m2, n) of each chunk
+// ws_wf: [rows][nchunks][3] = (mean, m2, n) of each chunk.  A thread reduces
+// batches of kUnroll vectors exactly (two passes over registers, fp32x2 lanes)
+// and folds each batch into its running triple with one Chan merge.
 template <typename T, int EPV>
 __global__ void __launch_bounds__(kBlock)
     r2_stats_fwd_kernel(const T* __restrict__ x, int64_t D, int64_t chunk, int nchunks,
                         float* __restrict__ ws_wf) {
+  using M = typename MathSel<EPV>::M;
+  using E = typename M::E;
+  constexpr int NE = MathSel<EPV>::NE;
   __shared__ WF sm[kBlock / 32];
   const int64_t row = blockIdx.x;
+  const int64_t step = static_cast<int64_t>(kBlock) * EPV;
   for (int c = blockIdx.y; c < nchunks; c += gridDim.y) {
     const int64_t d0 = static_cast<int64_t>(c) * chunk;
     const int64_t d1 = d0 + chunk < D ? d0 + chunk : D;
     WF acc = {0.f, 0.f, 0.f};
-    const int64_t step = static_cast<int64_t>(kBlock) * EPV;
-    for (int64_t d = d0 + static_cast<int64_t>(threadIdx.x) * EPV; d < d1; d += kUnroll * step) {
-      Pack<T, EPV> p[kUnroll];
+    const T* p = x + row * D + d0 + static_cast<int64_t>(threadIdx.x) * EPV;
+    int64_t d = d0 + static_cast<int64_t>(threadIdx.x) * EPV;
+    for (; d + (kUnroll - 1) * step < d1; d += kUnroll * step, p += kUnroll * step) {
+      Pack<T, EPV> pk[kUnroll];
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u)
-        if (d + u * step < d1) p[u] = load_stream<T, EPV>(x, row * D + d + u * step);
+      for (int u = 0; u < kUnroll; ++u) pk[u] = load_keep<T, EPV>(p + u * step);
+      E v[kUnroll][NE];
+      E sum = M::bcast(0.f);
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
-        if (d + u * step < d1) {
-          float v[EPV];
+        unpack<T, EPV>(pk[u], v[u]);
 #pragma unroll
-          for (int e = 0; e < EPV; ++e) v[e] = Cvt<T>::to_f32(p[u].v[e]);
-          wf_add_batch<EPV>(acc, v);
-        }
+        for (int e = 0; e < NE; ++e) sum = M::add(sum, v[u][e]);
       }
+      WF b;
+      b.n = static_cast<float>(kUnroll * EPV);
+      b.mean = M::hsum(sum) * (1.0f / (kUnroll * EPV));
+      const E bm = M::bcast(b.mean);
+      E q = M::bcast(0.f);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+        for (int e = 0; e < NE; ++e) {
+          const E dl = lane_sub<M>(v[u][e], bm);
+          q = M::fma(dl, dl, q);
+        }
+      b.m2 = M::hsum(q);
+      acc = wf_merge(acc, b);
+    }
+    for (; d < d1; d += step, p += step) {
+      const Pack<T, EPV> pk = load_keep<T, EPV>(p);
+      float v[EPV];
+#pragma unroll
+      for (int e = 0; e < EPV; ++e) v[e] = Cvt<T>::to_f32(pk.v[e]);
+      wf_add_batch<EPV>(acc, v);
     }
     const WF t = wf_block_reduce(acc, sm);
     if (threadIdx.x == 0) {
@@ -154,19 +189,33 @@ __global__ void __launch_bounds__(kBlock)
   }
 }
 
+// One warp per row: lane l merges chunks l, l+32, ... in increasing order, then a
+// fixed-pairing butterfly merges the 32 lanes.
 __global__ void r2_finalize_fwd_kernel(const float* __restrict__ ws_wf, int64_t rows, int nchunks,
                                        float eps, float* __restrict__ mean,
                                        float* __restrict__ ivar) {
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (row >= rows) return;
   WF t = {0.f, 0.f, 0.f};
-  for (int c = 0; c < nchunks; ++c) {
+  for (int c = lane; c < nchunks; c += 32) {
     const float* p = ws_wf + (row * nchunks + c) * 3;
     WF b = {p[0], p[1], p[2]};
     t = wf_merge(t, b);
   }
-  mean[row] = t.mean;
-  ivar[row] = 1.0f / sqrtf(t.m2 / t.n + eps);
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    WF o;
+    o.mean = __shfl_xor_sync(0xffffffffu, t.mean, off);
+    o.m2 = __shfl_xor_sync(0xffffffffu, t.m2, off);
+    o.n = __shfl_xor_sync(0xffffffffu, t.n, off);
+    const bool low = (lane & off) == 0;
+    t = low ? wf_merge(t, o) : wf_merge(o, t);
+  }
+  if (lane == 0) {
+    mean[row] = t.mean;
+    ivar[row] = 1.0f / sqrtf(t.m2 / t.n + eps);
+  }
 }
 
 template <typename T, int EPV, bool ROW_AFFINE>
@@ -175,6 +224,9 @@ __global__ void __launch_bounds__(kBlock)
                         const float* __restrict__ beta, const float* __restrict__ mean,
                         const float* __restrict__ ivar, int64_t D, int64_t C, int64_t chunk,
                         int nchunks, T* y) {
+  using M = typename MathSel<EPV>::M;
+  using E = typename M::E;
+  constexpr int NE = MathSel<EPV>::NE;
   const int64_t row = blockIdx.x;
   const float mu = mean[row], iv = ivar[row];
   float gr = 1.f, br = 0.f;
@@ -182,35 +234,34 @@ __global__ void __launch_bounds__(kBlock)
     gr = gamma[row % C];
     br = beta[row % C];
   }
-  const float sc = iv * gr;
+  const E nmu = M::bcast(-mu), iv2 = M::bcast(iv), sc2 = M::bcast(iv * gr), br2 = M::bcast(br);
   const int64_t step = static_cast<int64_t>(kBlock) * EPV;
   for (int c = blockIdx.y; c < nchunks; c += gridDim.y) {
     const int64_t d0 = static_cast<int64_t>(c) * chunk;
     const int64_t d1 = d0 + chunk < D ? d0 + chunk : D;
     for (int64_t d = d0 + static_cast<int64_t>(threadIdx.x) * EPV; d < d1; d += kUnroll * step) {
-      Pack<T, EPV> p[kUnroll];
+      const T* p = x + row * D + d;
+      T* q = y + row * D + d;
+      Pack<T, EPV> pk[kUnroll];
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u)
-        if (d + u * step < d1) p[u] = load_stream<T, EPV>(x, row * D + d + u * step);
+        if (d + u * step < d1) pk[u] = load_stream<T, EPV>(p + u * step, 0);
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
-        const int64_t dd = d + u * step;
-        if (dd < d1) {
-          Pack<T, EPV> o;
+        if (d + u * step < d1) {
+          E v[NE], o[NE];
+          unpack<T, EPV>(pk[u], v);
           if constexpr (ROW_AFFINE) {
 #pragma unroll
-            for (int e = 0; e < EPV; ++e)
-              o.v[e] = Cvt<T>::from_f32(fmaf(Cvt<T>::to_f32(p[u].v[e]) - mu, sc, br));
+            for (int e = 0; e < NE; ++e) o[e] = M::fma(M::add(v[e], nmu), sc2, br2);
           } else {
-            float g[EPV], b[EPV];
-            load_params<EPV>(gamma, dd, g);
-            load_params<EPV>(beta, dd, b);
+            E g[NE], b[NE];
+            load_param_lanes<EPV>(gamma, d + u * step, g);
+            load_param_lanes<EPV>(beta, d + u * step, b);
 #pragma unroll
-            for (int e = 0; e < EPV; ++e)
-              o.v[e] =
-                  Cvt<T>::from_f32(fmaf((Cvt<T>::to_f32(p[u].v[e]) - mu) * iv, g[e], b[e]));
+            for (int e = 0; e < NE; ++e) o[e] = M::fma(M::mul(M::add(v[e], nmu), iv2), g[e], b[e]);
           }
-          store_stream<T, EPV>(y, row * D + dd, o);
+          store_stream<T, EPV>(q + u * step, 0, repack<T, EPV>(o));
         }
       }
     }
@@ -224,40 +275,47 @@ __global__ void __launch_bounds__(kBlock)
                         const float* __restrict__ gamma, const float* __restrict__ mean,
                         const float* __restrict__ ivar, int64_t D, int64_t chunk, int nchunks,
                         float* __restrict__ ws_sums) {
+  using M = typename MathSel<EPV>::M;
+  using E = typename M::E;
+  constexpr int NE = MathSel<EPV>::NE;
   __shared__ float sm[2 * (kBlock / 32)];
   const int64_t row = blockIdx.x;
-  const float mu = mean[row], iv = ivar[row];
+  const E nmu = M::bcast(-mean[row]), iv2 = M::bcast(ivar[row]);
   const int64_t step = static_cast<int64_t>(kBlock) * EPV;
   for (int c = blockIdx.y; c < nchunks; c += gridDim.y) {
     const int64_t d0 = static_cast<int64_t>(c) * chunk;
     const int64_t d1 = d0 + chunk < D ? d0 + chunk : D;
-    float r[2] = {0.f, 0.f};
+    E a0 = M::bcast(0.f), a1 = M::bcast(0.f);
     for (int64_t d = d0 + static_cast<int64_t>(threadIdx.x) * EPV; d < d1; d += kUnroll * step) {
-      Pack<T, EPV> px[kUnroll], pd[kUnroll];
+      const T* px = x + row * D + d;
+      const T* pd = dy + row * D + d;
+      Pack<T, EPV> kx[kUnroll], kd[kUnroll];
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
         if (d + u * step < d1) {
-          px[u] = load_stream<T, EPV>(x, row * D + d + u * step);
-          pd[u] = load_stream<T, EPV>(dy, row * D + d + u * step);
+          kx[u] = load_keep<T, EPV>(px + u * step);
+          kd[u] = load_keep<T, EPV>(pd + u * step);
         }
       }
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
-        const int64_t dd = d + u * step;
-        if (dd < d1) {
-          float g[EPV];
-          if constexpr (!ROW_AFFINE) load_params<EPV>(gamma, dd, g);
+        if (d + u * step < d1) {
+          E vx[NE], vd[NE], g[NE];
+          unpack<T, EPV>(kx[u], vx);
+          unpack<T, EPV>(kd[u], vd);
+          if constexpr (!ROW_AFFINE) load_param_lanes<EPV>(gamma, d + u * step, g);
 #pragma unroll
-          for (int e = 0; e < EPV; ++e) {
-            const float xh = (Cvt<T>::to_f32(px[u].v[e]) - mu) * iv;
-            float gy = Cvt<T>::to_f32(pd[u].v[e]);
-            if constexpr (!ROW_AFFINE) gy *= g[e];
-            r[0] += gy;
-            r[1] = fmaf(gy, xh, r[1]);
+          for (int e = 0; e < NE; ++e) {
+            const E xh = M::mul(M::add(vx[e], nmu), iv2);
+            E gy = vd[e];
+            if constexpr (!ROW_AFFINE) gy = M::mul(gy, g[e]);
+            a0 = M::add(a0, gy);
+            a1 = M::fma(gy, xh, a1);
           }
         }
       }
     }
+    float r[2] = {M::hsum(a0), M::hsum(a1)};
     sum_block_reduce<2>(r, sm);
     if (threadIdx.x == 0) {
       float* o = ws_sums + (row * nchunks + c) * 2;
@@ -269,24 +327,33 @@ __global__ void __launch_bounds__(kBlock)
 
 // coef: [rows][2] = (sum gy / D, sum gy*xhat / D).  With ROW_AFFINE the raw sums
 // are also written as the per-(n, c) dgamma / dbeta partials, laid out [n][2][C].
+// One warp per row, chunks summed lane-strided then by a butterfly (fixed order).
 template <bool ROW_AFFINE>
 __global__ void r2_finalize_bwd_kernel(const float* __restrict__ ws_sums, int64_t rows,
                                        int nchunks, int64_t D, int64_t C,
                                        float* __restrict__ coef, float* __restrict__ part) {
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (row >= rows) return;
   float r0 = 0.f, r1 = 0.f;
-  for (int c = 0; c < nchunks; ++c) {
+  for (int c = lane; c < nchunks; c += 32) {
     r0 += ws_sums[(row * nchunks + c) * 2 + 0];
     r1 += ws_sums[(row * nchunks + c) * 2 + 1];
   }
-  const float inv_D = 1.0f / static_cast<float>(D);
-  coef[row * 2 + 0] = r0 * inv_D;
-  coef[row * 2 + 1] = r1 * inv_D;
-  if constexpr (ROW_AFFINE) {
-    const int64_t n = row / C, ch = row - n * C;
-    part[(n * 2 + 0) * C + ch] = r1;
-    part[(n * 2 + 1) * C + ch] = r0;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    r0 += __shfl_xor_sync(0xffffffffu, r0, off);
+    r1 += __shfl_xor_sync(0xffffffffu, r1, off);
+  }
+  if (lane == 0) {
+    const float inv_D = 1.0f / static_cast<float>(D);
+    coef[row * 2 + 0] = r0 * inv_D;
+    coef[row * 2 + 1] = r1 * inv_D;
+    if constexpr (ROW_AFFINE) {
+      const int64_t n = row / C, ch = row - n * C;
+      part[(n * 2 + 0) * C + ch] = r1;
+      part[(n * 2 + 1) * C + ch] = r0;
+    }
   }
 }
 
@@ -298,35 +365,41 @@ __global__ void __launch_bounds__(kBlock)
                                const float* __restrict__ ivar, const float* __restrict__ coef,
                                int64_t D, int64_t C, int64_t chunk, int nchunks,
                                T* __restrict__ dx) {
+  using M = typename MathSel<EPV>::M;
+  using E = typename M::E;
+  constexpr int NE = MathSel<EPV>::NE;
   const int64_t row = blockIdx.x;
-  const float mu = mean[row], iv = ivar[row];
-  const float sc = iv * gamma[row % C];
-  const float m0 = coef[row * 2 + 0], m1 = coef[row * 2 + 1];
+  const float iv = ivar[row];
+  const E nmu = M::bcast(-mean[row]), iv2 = M::bcast(iv), sc2 = M::bcast(iv * gamma[row % C]);
+  const E nm0 = M::bcast(-coef[row * 2 + 0]), nm1 = M::bcast(-coef[row * 2 + 1]);
   const int64_t step = static_cast<int64_t>(kBlock) * EPV;
   for (int c = blockIdx.y; c < nchunks; c += gridDim.y) {
     const int64_t d0 = static_cast<int64_t>(c) * chunk;
     const int64_t d1 = d0 + chunk < D ? d0 + chunk : D;
     for (int64_t d = d0 + static_cast<int64_t>(threadIdx.x) * EPV; d < d1; d += kUnroll * step) {
-      Pack<T, EPV> px[kUnroll], pd[kUnroll];
+      const T* px = x + row * D + d;
+      const T* pd = dy + row * D + d;
+      T* po = dx + row * D + d;
+      Pack<T, EPV> kx[kUnroll], kd[kUnroll];
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
         if (d + u * step < d1) {
-          px[u] = load_stream<T, EPV>(x, row * D + d + u * step);
-          pd[u] = load_stream<T, EPV>(dy, row * D + d + u * step);
+          kx[u] = load_stream<T, EPV>(px + u * step, 0);
+          kd[u] = load_stream<T, EPV>(pd + u * step, 0);
         }
       }
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
-        const int64_t dd = d + u * step;
-        if (dd < d1) {
-          Pack<T, EPV> o;
+        if (d + u * step < d1) {
+          E vx[NE], vd[NE], o[NE];
+          unpack<T, EPV>(kx[u], vx);
+          unpack<T, EPV>(kd[u], vd);
 #pragma unroll
-          for (int e = 0; e < EPV; ++e) {
-            const float xh = (Cvt<T>::to_f32(px[u].v[e]) - mu) * iv;
-            const float gy = Cvt<T>::to_f32(pd[u].v[e]);
-            o.v[e] = Cvt<T>::from_f32(sc * (gy - fmaf(xh, m1, m0)));
+          for (int e = 0; e < NE; ++e) {
+            const E xh = M::mul(M::add(vx[e], nmu), iv2);
+            o[e] = M::mul(M::add(vd[e], M::fma(xh, nm1, nm0)), sc2);
           }
-          store_stream<T, EPV>(dx, row * D + dd, o);
+          store_stream<T, EPV>(po + u * step, 0, repack<T, EPV>(o));
         }
       }
     }
@@ -335,7 +408,10 @@ __global__ void __launch_bounds__(kBlock)
 
 // LayerNorm: a thread owns EPV columns and walks the rows of its slice, so the
 // dgamma / dbeta contributions accumulate in registers.  grid = (column blocks,
-// row slices); one partial row [2][D] per slice.
+// row slices); one partial row [2][D] per slice.  The four per-row scalars are
+// staged through shared memory, kRowTile rows at a time.
+constexpr int kRowTile = 128;
+
 template <typename T, int EPV>
 __global__ void __launch_bounds__(kBlock)
     r2_apply_bwd_ln_kernel(const T* __restrict__ dy, const T* __restrict__ x,
@@ -343,33 +419,66 @@ __global__ void __launch_bounds__(kBlock)
                            const float* __restrict__ ivar, const float* __restrict__ coef,
                            int64_t N, int64_t D, int64_t rows_per_slice, T* __restrict__ dx,
                            float* __restrict__ part) {
+  using M = typename MathSel<EPV>::M;
+  using E = typename M::E;
+  constexpr int NE = MathSel<EPV>::NE;
+  __shared__ float4 rowc[kRowTile];  // (-mean, ivar, -m0, -m1)
   const int64_t col = (static_cast<int64_t>(blockIdx.x) * kBlock + threadIdx.x) * EPV;
-  if (col >= D) return;
+  const bool live = col < D;
   const int64_t slice = blockIdx.y;
   const int64_t r0 = slice * rows_per_slice;
   const int64_t r1 = r0 + rows_per_slice < N ? r0 + rows_per_slice : N;
-  float g[EPV], dg[EPV], db[EPV];
-  load_params<EPV>(gamma, col, g);
+  E g[NE], dg[NE], db[NE];
+  if (live) load_param_lanes<EPV>(gamma, col, g);
 #pragma unroll
-  for (int e = 0; e < EPV; ++e) dg[e] = db[e] = 0.f;
-  for (int64_t row = r0; row < r1; ++row) {
-    const Pack<T, EPV> px = load_stream<T, EPV>(x, row * D + col);
-    const Pack<T, EPV> pd = load_stream<T, EPV>(dy, row * D + col);
-    const float mu = __ldg(mean + row), iv = __ldg(ivar + row);
-    const float m0 = __ldg(coef + row * 2), m1 = __ldg(coef + row * 2 + 1);
-    Pack<T, EPV> o;
-#pragma unroll
-    for (int e = 0; e < EPV; ++e) {
-      const float xh = (Cvt<T>::to_f32(px.v[e]) - mu) * iv;
-      const float dv = Cvt<T>::to_f32(pd.v[e]);
-      dg[e] = fmaf(dv, xh, dg[e]);
-      db[e] += dv;
-      o.v[e] = Cvt<T>::from_f32(iv * (dv * g[e] - fmaf(xh, m1, m0)));
+  for (int e = 0; e < NE; ++e) dg[e] = db[e] = M::bcast(0.f);
+  for (int64_t base = r0; base < r1; base += kRowTile) {
+    const int tile = static_cast<int>(r1 - base < kRowTile ? r1 - base : kRowTile);
+    __syncthreads();
+    if (threadIdx.x < tile) {
+      const int64_t row = base + threadIdx.x;
+      rowc[threadIdx.x] = make_float4(-mean[row], ivar[row], -coef[row * 2], -coef[row * 2 + 1]);
     }
-    store_stream<T, EPV>(dx, row * D + col, o);
+    __syncthreads();
+    if (live) {
+      const T* px = x + base * D + col;
+      const T* pd = dy + base * D + col;
+      T* po = dx + base * D + col;
+      for (int i = 0; i < tile; i += 2) {
+        Pack<T, EPV> kx[2], kd[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (i + u < tile) {
+            kx[u] = load_stream<T, EPV>(px + (i + u) * D, 0);
+            kd[u] = load_stream<T, EPV>(pd + (i + u) * D, 0);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (i + u < tile) {
+            const float4 rc = rowc[i + u];
+            const E nmu = M::bcast(rc.x), iv2 = M::bcast(rc.y);
+            const E nm0 = M::bcast(rc.z), nm1 = M::bcast(rc.w);
+            E vx[NE], vd[NE], o[NE];
+            unpack<T, EPV>(kx[u], vx);
+            unpack<T, EPV>(kd[u], vd);
+#pragma unroll
+            for (int e = 0; e < NE; ++e) {
+              const E xh = M::mul(M::add(vx[e], nmu), iv2);
+              dg[e] = M::fma(vd[e], xh, dg[e]);
+              db[e] = M::add(db[e], vd[e]);
+              o[e] = M::mul(M::add(M::mul(vd[e], g[e]), M::fma(xh, nm1, nm0)), iv2);
+            }
+            store_stream<T, EPV>(po + (i + u) * D, 0, repack<T, EPV>(o));
+          }
+        }
+      }
+    }
   }
-  store_params<EPV>(part + (slice * 2 + 0) * D, col, dg);
-  store_params<EPV>(part + (slice * 2 + 1) * D, col, db);
+  if (live) {
+    store_param_lanes<EPV>(part + (slice * 2 + 0) * D, col, dg);
+    store_param_lanes<EPV>(part + (slice * 2 + 1) * D, col, db);
+  }
 }
 
 // ===========================================================================
@@ -394,12 +503,6 @@ __device__ __forceinline__ int64_t s2_item(const S2Geom& gm) {
 }
 __device__ __forceinline__ int s2_chunk(const S2Geom& gm) {
   return gm.reverse ? (gm.nchunks - 1 - static_cast<int>(blockIdx.x)) : static_cast<int>(blockIdx.x);
-}
-
-// a - b on math lanes
-template <typename M>
-__device__ __forceinline__ typename M::E lane_sub(typename M::E a, typename M::E b) {
-  return M::fma(b, M::bcast(-1.f), a);
 }
 
 // Per-thread geometry of the S2 kernels: which channel vector and which voxels
@@ -857,7 +960,7 @@ R2Plan r2_plan(int64_t rows, int64_t D, int epv, bool ln_bwd) {
   p.grid_y = p.nchunks < 65535 ? p.nchunks : 65535;
   if (ln_bwd) {
     const int64_t colblocks = ceil_div(D, static_cast<int64_t>(kBlock) * epv);
-    int64_t slices = ceil_div(static_cast<int64_t>(sms) * 4, colblocks);
+    int64_t slices = ceil_div(static_cast<int64_t>(sms) * 2, colblocks);
     if (slices > rows) slices = rows;
     if (slices > 65535) slices = 65535;
     if (slices < 1) slices = 1;
@@ -873,7 +976,7 @@ static cudaError_t r2_fwd_t(const R2Args& a, const R2Plan& p, cudaStream_t s) {
   r2_stats_fwd_kernel<T, EPV><<<grid, kBlock, 0, s>>>(static_cast<const T*>(a.x), a.D, p.chunk,
                                                       p.nchunks, a.ws_part);
   NVN_LAUNCHED();
-  r2_finalize_fwd_kernel<<<static_cast<unsigned>(ceil_div(a.rows, 128)), 128, 0, s>>>(
+  r2_finalize_fwd_kernel<<<static_cast<unsigned>(ceil_div(a.rows, 4)), 128, 0, s>>>(
       a.ws_part, a.rows, p.nchunks, a.eps, a.mean, a.ivar);
   NVN_LAUNCHED();
   if (a.row_affine) {
@@ -899,7 +1002,7 @@ static cudaError_t r2_bwd_t(const R2Args& a, const R2Plan& p, cudaStream_t s) {
     r2_stats_bwd_kernel<T, EPV, true><<<grid, kBlock, 0, s>>>(dy, x, a.gamma, a.mean, a.ivar,
                                                               a.D, p.chunk, p.nchunks, a.ws_part);
     NVN_LAUNCHED();
-    r2_finalize_bwd_kernel<true><<<static_cast<unsigned>(ceil_div(a.rows, 128)), 128, 0, s>>>(
+    r2_finalize_bwd_kernel<true><<<static_cast<unsigned>(ceil_div(a.rows, 4)), 128, 0, s>>>(
         a.ws_part, a.rows, p.nchunks, a.D, a.C, a.ws_coef, a.ws_colpart);
     NVN_LAUNCHED();
     r2_apply_bwd_affine_kernel<T, EPV><<<grid, kBlock, 0, s>>>(
@@ -909,7 +1012,7 @@ static cudaError_t r2_bwd_t(const R2Args& a, const R2Plan& p, cudaStream_t s) {
     r2_stats_bwd_kernel<T, EPV, false><<<grid, kBlock, 0, s>>>(
         dy, x, a.gamma, a.mean, a.ivar, a.D, p.chunk, p.nchunks, a.ws_part);
     NVN_LAUNCHED();
-    r2_finalize_bwd_kernel<false><<<static_cast<unsigned>(ceil_div(a.rows, 128)), 128, 0, s>>>(
+    r2_finalize_bwd_kernel<false><<<static_cast<unsigned>(ceil_div(a.rows, 4)), 128, 0, s>>>(
         a.ws_part, a.rows, p.nchunks, a.D, a.C, a.ws_coef, nullptr);
     NVN_LAUNCHED();
     const dim3 g2(static_cast<unsigned>(ceil_div(a.D, static_cast<int64_t>(kBlock) * EPV)),
