@@ -24,6 +24,7 @@ NVN_ERR_WORKSPACE = -6
 NVN_ERR_CUDA = -7
 NVN_ERR_UNSUPPORTED = -8
 NVN_ERR_LIMIT = -9
+NVN_ERR_TIMEOUT = -10
 
 _c = ctypes
 _i64 = _c.c_int64
@@ -37,6 +38,7 @@ SIGNATURES = {
     "nvn_status_string": (_c.c_char_p, [_int]),
     "nvn_last_cuda_error": (_int, []),
     "nvn_launch_count": (_c.c_uint64, []),
+    "nvn_device_status": (_int, []),
     "nvn_ln_dims": (_int, [_int, _c.POINTER(_i64), _int, _c.POINTER(_int), _c.POINTER(_i64),
                            _c.POINTER(_i64)]),
     "nvn_in_dims": (_int, [_int, _c.POINTER(_i64), _c.c_char_p, _c.POINTER(_i64), _c.POINTER(_i64),

@@ -274,6 +274,61 @@ __device__ __forceinline__ void store_param_lanes(
 }
 
 // ---------------------------------------------------------------------------
+// Bulk asynchronous copies (TMA, non-tensor form) into a shared-memory ring.
+//
+// cp.async.bulk moves a contiguous, 16-byte aligned block global -> shared without
+// touching registers and signals an mbarrier with the number of bytes written.  The
+// row kernels use it to keep several row batches in flight per CTA independently of
+// the register budget.  No multicast form is used anywhere.
+//
+// Waits are bounded: a wait that does not complete within kMbarPollLimit polls gives
+// up and reports it; the caller then stops issuing copies, finishes its loop on
+// whatever is in shared memory and raises the device status word, so a mistake in
+// the byte accounting shows up as an error status and never as a hung GPU.
+// ---------------------------------------------------------------------------
+constexpr unsigned kMbarPollLimit = 1u << 22;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+  return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, unsigned bytes,
+                                          uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(smem_u32(smem_dst)),
+      "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+// true when the phase with the given parity has completed
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity) {
+  const unsigned addr = smem_u32(bar);
+  for (unsigned i = 0; i < kMbarPollLimit; ++i) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+// ---------------------------------------------------------------------------
 // Row-group all-reduce (sum) of NV values.
 //
 // A "row group" is TPR consecutive threads of a CTA (TPR a power of two).  For

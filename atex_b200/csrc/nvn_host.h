@@ -27,6 +27,7 @@ struct RowsArgs {
   int64_t D;
   int64_t C;
   float eps;
+  int* status;  // device status word: set non-zero when a bounded wait gave up
 };
 
 struct RowsPlan {
@@ -37,17 +38,21 @@ struct RowsPlan {
   int vpt;
   int epv;
   int rb;
+  int load_mode;  // 0 plain, 1 register prefetch, >= 2 TMA ring with that many stages
   int partial_rows;  // rows of [2][D] dgamma/dbeta partials the backward kernel writes
 };
 
 int device_sm_count();
 void count_launch();
+// Device address of the library's status word on the current device (nullptr on failure).
+int* device_status_word();
 
 // Row-group shapes: X(index, TPR, VPT, CS, RB, PR, MINB, PF)
 //   TPR threads per row, VPT vectors per thread, CS CTAs per cluster, RB rows in
 //   flight per row group, PR gamma/beta cached in registers, MINB minimum CTAs per
-//   SM requested from the compiler (0 = no request), PF software prefetch of the
-//   next row batch.
+//   SM requested from the compiler (0 = no request), PF load mode: 0 = plain loads,
+//   1 = register prefetch of the next row batch, >= 2 = TMA (cp.async.bulk) ring in
+//   shared memory with that many stages.
 // "Light" kernels keep only the row itself in registers (LayerNorm forward,
 // InstanceNorm forward/backward); "heavy" is LayerNorm backward, which adds the
 // per-column dgamma/dbeta accumulators and therefore spreads a row over more
@@ -55,10 +60,10 @@ void count_launch();
 // first entry (in listing order) among those of the smallest sufficient capacity.
 #ifndef NVN_ROW_SHAPES_LIGHT
 #define NVN_ROW_SHAPES_LIGHT(X)                                                              \
-  X(0, 4, 1, 1, 4, 1, 0, 1)     X(1, 8, 1, 1, 4, 1, 0, 1)     X(2, 16, 1, 1, 4, 1, 0, 1)     \
-  X(3, 32, 1, 1, 4, 1, 0, 1)    X(4, 32, 2, 1, 2, 1, 0, 1)    X(5, 32, 4, 1, 2, 1, 0, 1)     \
-  X(6, 128, 2, 1, 1, 1, 0, 1)   X(7, 256, 2, 1, 2, 1, 0, 1)   X(8, 256, 4, 1, 1, 0, 0, 1)    \
-  X(9, 512, 4, 1, 1, 0, 0, 1)   X(10, 512, 8, 1, 1, 0, 0, 1)  X(11, 256, 8, 4, 1, 0, 0, 1)   \
+  X(0, 4, 1, 1, 4, 1, 0, 1)     X(1, 8, 1, 1, 4, 1, 0, 1)     X(2, 16, 1, 1, 4, 1, 0, 3)     \
+  X(3, 32, 1, 1, 4, 1, 0, 3)    X(4, 32, 2, 1, 2, 1, 0, 3)    X(5, 32, 4, 1, 2, 1, 0, 3)     \
+  X(6, 128, 2, 1, 1, 1, 0, 1)   X(7, 128, 4, 1, 1, 1, 0, 2)   X(8, 256, 4, 1, 1, 0, 0, 2)    \
+  X(9, 512, 4, 1, 1, 0, 0, 2)   X(10, 512, 8, 1, 1, 0, 0, 1)  X(11, 256, 8, 4, 1, 0, 0, 2)   \
   X(12, 512, 8, 4, 1, 0, 0, 1)  X(13, 512, 8, 8, 1, 0, 0, 1)  X(14, 512, 8, 16, 1, 0, 0, 1)
 #endif
 

@@ -199,6 +199,7 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
     a.D = D;
     a.C = C;
     a.eps = eps;
+    a.status = device_status_word();
     RowsPlan rp;
     cudaError_t e =
         rows_fn(dtype, bwd)(row_affine, p.scalar, p.shape, a, stream, false, &rp);
@@ -321,6 +322,28 @@ int device_sm_count() {
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
+namespace {
+// Raised by a kernel whose bounded wait on an asynchronous copy gave up.
+__device__ int g_status_word = 0;
+std::mutex g_status_mutex;
+int* g_status_ptr[64] = {};
+}  // namespace
+
+int* device_status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (g_status_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    g_status_ptr[dev] = static_cast<int*>(p);
+  }
+  return g_status_ptr[dev];
+}
+
 }  // namespace nvn
 
 using namespace nvn;
@@ -351,6 +374,8 @@ const char* nvn_status_string(int status) {
       return "problem size not supported";
     case NVN_ERR_LIMIT:
       return "problem size exceeds a built-in capacity";
+    case NVN_ERR_TIMEOUT:
+      return "a kernel gave up waiting for an asynchronous copy";
     default:
       return "unknown status";
   }
@@ -359,6 +384,18 @@ const char* nvn_status_string(int status) {
 int nvn_last_cuda_error(void) { return t_last_cuda_error; }
 
 uint64_t nvn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int nvn_device_status(void) {
+  int* p = device_status_word();
+  if (p == nullptr) return NVN_ERR_CUDA;
+  int v = 0;
+  // synchronous on purpose: a diagnostic, not part of the asynchronous call path
+  if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return NVN_ERR_CUDA;
+  }
+  return v == 0 ? NVN_OK : NVN_ERR_TIMEOUT;
+}
 
 int nvn_ln_dims(int rank, const int64_t* dims, int n_axis, const int* axis, int64_t* N,
                 int64_t* D) {
@@ -537,9 +574,10 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
              p.scalar ? 1 : full_epv(dtype), static_cast<long long>(p.r2.chunk), p.r2.nchunks,
              p.r2.slices);
   } else {
-    snprintf(out, out_bytes, "rows tpr=%d vpt=%d cluster=%d rb=%d epv=%d block=%d grid=%d",
-             p.rows.tpr, p.rows.vpt, p.rows.cluster, p.rows.rb, p.rows.epv, p.rows.block,
-             p.rows.grid);
+    snprintf(out, out_bytes, "rows tpr=%d vpt=%d cluster=%d rb=%d load=%s%d epv=%d block=%d grid=%d",
+             p.rows.tpr, p.rows.vpt, p.rows.cluster, p.rows.rb,
+             p.rows.load_mode >= 2 ? "tma" : (p.rows.load_mode == 1 ? "prefetch" : "plain"),
+             p.rows.load_mode >= 2 ? p.rows.load_mode : 0, p.rows.epv, p.rows.block, p.rows.grid);
   }
   return NVN_OK;
 }

@@ -47,9 +47,12 @@ struct RowBlock {
 //   PR    keep gamma (and beta) for the thread's columns in registers for the whole
 //         kernel instead of re-reading them (L1 / L2 hits) for every row
 //   MINB  minimum resident CTAs per SM asked of the compiler (register cap)
-//   PF    software prefetch: the loads of the next row batch are issued as soon as the
-//         current batch has been converted to fp32, so they are in flight during the
-//         reductions and the stores
+//   PF    load mode.  0: plain loads at the top of each iteration.  1: register prefetch -
+//         the loads of the next row batch are issued as soon as the current batch has been
+//         converted to fp32, so they are in flight during the reductions and the stores.
+//         >= 2: a shared-memory ring of PF stages filled by cp.async.bulk (TMA); one thread
+//         issues whole row batches, mbarriers signal arrival, and the bytes in flight no
+//         longer depend on registers or occupancy.
 //
 // All element-wise math runs on fp32x2 lanes (nvn::P2) when EPV is even.
 
@@ -89,23 +92,149 @@ __device__ __forceinline__ void load_tile(const Pack<T, EPV>* __restrict__ src, 
   }
 }
 
+// Shared-memory ring of the TMA load mode.  A stage holds one row batch of this CTA:
+// RPC*RB consecutive rows when a CTA owns whole rows (CS == 1), or RB row slices of
+// D/CS elements when a cluster shares the rows.  NT tensors (x, or x and dy) sit one after
+// the other inside a stage.
+template <typename T, int EPV, int VPT, int RB, int RPC, int CS, int STAGES, int NT>
+struct RowRing {
+  unsigned char* base;
+  uint64_t* full;       // [STAGES]
+  unsigned stage_bytes;
+  unsigned tensor_bytes;  // bytes of one tensor inside a stage
+  unsigned row_bytes;     // bytes of one row (CS == 1) or one row slice (CS > 1)
+  bool dead;              // a wait gave up: stop issuing and stop waiting
+
+  __device__ __forceinline__ void init(unsigned char* smem, uint64_t* bars, int64_t D) {
+    base = smem;
+    full = bars;
+    row_bytes = static_cast<unsigned>((D / CS) * sizeof(T));
+    tensor_bytes = row_bytes * (CS == 1 ? RPC * RB : RB);
+    stage_bytes = tensor_bytes * NT;
+    dead = false;
+    if (threadIdx.x == 0) {
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
+      mbar_init_fence();
+    }
+    __syncthreads();
+  }
+
+  // Called by one thread: start the copies of the batch whose first row is `row_first`
+  // (the CTA's batch base, without the row-group offset) into stage `s`.
+  __device__ __forceinline__ void issue(int s, const T* const (&src)[NT], int64_t row_first,
+                                        int64_t N, int64_t D, unsigned crank) {
+    unsigned char* dst = base + static_cast<size_t>(s) * stage_bytes;
+    if constexpr (CS == 1) {
+      const int64_t left = N - row_first;
+      const unsigned rows = static_cast<unsigned>(left < RPC * RB ? left : RPC * RB);
+      const unsigned bytes = rows * row_bytes;
+      mbar_expect_tx(&full[s], bytes * NT);
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+        bulk_load(dst + t * tensor_bytes, src[t] + row_first * D, bytes, &full[s]);
+    } else {
+      const int64_t left = N - row_first;
+      const unsigned rows = static_cast<unsigned>(left < RB ? left : RB);
+      mbar_expect_tx(&full[s], rows * row_bytes * NT);
+      const int64_t slice = (D / CS) * static_cast<int64_t>(crank);
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+        for (unsigned r = 0; r < rows; ++r)
+          bulk_load(dst + t * tensor_bytes + r * row_bytes, src[t] + (row_first + r) * D + slice,
+                    row_bytes, &full[s]);
+    }
+  }
+
+  __device__ __forceinline__ bool wait(int s, unsigned use) {
+    if (dead) return true;
+    return mbar_wait_bounded(&full[s], use & 1u);
+  }
+
+  // Vector v of row-slot r of tensor t for this thread; `slot_vec` is the thread's first
+  // vector inside a row (slice) and consecutive vectors of a thread are VSTRIDE apart.
+  template <int VSTRIDE>
+  __device__ __forceinline__ Pack<T, EPV> read(int s, int t, int rowslot, int slot_vec,
+                                               int v) const {
+    const unsigned char* p = base + static_cast<size_t>(s) * stage_bytes + t * tensor_bytes +
+                             static_cast<size_t>(rowslot) * row_bytes;
+    return *reinterpret_cast<const Pack<T, EPV>*>(p + (static_cast<size_t>(slot_vec) +
+                                                       static_cast<size_t>(v) * VSTRIDE) *
+                                                          sizeof(Pack<T, EPV>));
+  }
+};
+
+// Per-thread view of a row: which vectors it owns.
+//   plain / register-prefetch modes: vector v of a thread is  v*TPR*CS + crank*TPR + lir
+//     (the CTAs of a cluster interleave, every access is a full coalesced segment);
+//   TMA mode in a cluster: every CTA owns one contiguous slice of D/CS elements (a single
+//     bulk copy per row), vector v is  crank*TPR*VPT + v*TPR + lir.
+template <int TPR, int VPT, int CS, bool TMA>
+struct VecMap {
+  static constexpr int kStride = (TMA && CS > 1) ? TPR : TPR * CS;
+  static __device__ __forceinline__ int first(unsigned crank, int lir) {
+    return (TMA && CS > 1) ? static_cast<int>(crank) * TPR * VPT + lir
+                           : static_cast<int>(crank) * TPR + lir;
+  }
+};
+
+// Tile of the current row batch out of ring stage `s` (TMA mode).
+template <typename T, int EPV, int VPT, int RB, int RPC, int CS, int TPR, bool EXACT, typename Ring>
+__device__ __forceinline__ void ring_tile(const Ring& ring, int s, int t, int64_t row_first,
+                                          int group, int lir, int64_t N, int nvalid,
+                                          RowTile<T, EPV, VPT, RB>& tile) {
+#pragma unroll
+  for (int r = 0; r < RB; ++r) {
+    const bool rv = row_first + r * RPC < N;
+    const int slot = CS == 1 ? r * RPC + group : r;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      if (rv && (EXACT || v < nvalid)) {
+        tile.p[r][v] = ring.template read<TPR>(s, t, slot, lir, v);
+      } else {
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) tile.p[r][v].v[e] = Cvt<T>::from_f32(0.f);
+      }
+    }
+  }
+}
+
+// After a bounded wait gave up: raise the status word and wait (bounded again) for the
+// copies that are still in flight, so none of them lands after the CTA has gone.
+template <typename Ring, int STAGES>
+__device__ __forceinline__ void ring_give_up(Ring& ring, int* status, int64_t j, int64_t nb) {
+  ring.dead = true;
+  if (threadIdx.x == 0) {
+    if (status != nullptr) atomicExch(status, 1);
+    const int64_t last = j + STAGES < nb ? j + STAGES : nb;
+    for (int64_t k = j; k < last; ++k)
+      (void)mbar_wait_bounded(&ring.full[k % STAGES], static_cast<unsigned>(k / STAGES) & 1u);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------
-template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, bool PF,
+template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, int PF,
           bool EXACT, bool ROW_AFFINE>
 __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
     rows_fwd_kernel(const RowsArgs a) {
   constexpr int BLOCK = RowBlock<TPR>::kBlock;
   constexpr int RPC = RowBlock<TPR>::kRowsPerCta;
-  constexpr int VSTRIDE = TPR * CS;
+  constexpr bool TMA = PF >= 2;
+  constexpr int STAGES = TMA ? PF : 1;
+  using Map = VecMap<TPR, VPT, CS, TMA>;
+  constexpr int VSTRIDE = Map::kStride;
   static_assert(CS == 1 || RPC == 1, "cluster kernels own one row per cluster");
+  static_assert(!(TMA && CS > 1) || EXACT, "cluster slices need rows that fill the shape");
   constexpr bool PARAMS_IN_REGS = !ROW_AFFINE && PR;
   using M = typename MathSel<EPV>::M;
   using E = typename M::E;
   constexpr int NE = MathSel<EPV>::NE;
   using P = Pack<T, EPV>;
 
+  extern __shared__ __align__(128) unsigned char ring_mem[];
+  __shared__ __align__(8) uint64_t ring_bars[STAGES];
   __shared__ ReduceSmem<RB, BLOCK> sm;
   int phase = 0;
 
@@ -119,10 +248,11 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
   const int64_t unit = blockIdx.x / CS;
   const int64_t nunits = gridDim.x / CS;
   const int64_t N = a.N;
-  const int64_t rowvecs = a.D / EPV;
-  const float inv_D = 1.0f / static_cast<float>(a.D);
+  const int64_t D = a.D;
+  const int64_t rowvecs = D / EPV;
+  const float inv_D = 1.0f / static_cast<float>(D);
   const float eps = a.eps;
-  const int vec0 = static_cast<int>(crank) * TPR + lir;
+  const int vec0 = Map::first(crank, lir);
   // number of this thread's vectors that fall inside the row (all VPT when EXACT)
   int nvalid = VPT;
   if constexpr (!EXACT) {
@@ -149,15 +279,36 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
   }
 
   const int64_t stride = nunits * (RPC * RB);
-  const int64_t first = unit * (RPC * RB) + group;
+  const int64_t batch0 = unit * (RPC * RB);  // first row of this CTA's first batch
+  const int64_t nb = batch0 < N ? (N - batch0 + stride - 1) / stride : 0;
   RowTile<T, EPV, VPT, RB> tile;
-  if constexpr (PF) load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, first, N, rowvecs, nvalid, tile);
-  for (int64_t row0 = first; row0 - group < N; row0 += stride) {
-    if constexpr (!PF)
+  RowRing<T, EPV, VPT, RB, RPC, CS, STAGES, 1> ring;
+  const T* const srcs[1] = {static_cast<const T*>(a.x)};
+  if constexpr (TMA) {
+    ring.init(ring_mem, ring_bars, D);
+    if (tid == 0) {
+      for (int64_t k = 0; k < STAGES && k < nb; ++k)
+        ring.issue(static_cast<int>(k), srcs, batch0 + k * stride, N, D, crank);
+    }
+  } else if constexpr (PF == 1) {
+    load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, batch0 + group, N, rowvecs, nvalid, tile);
+  }
+  for (int64_t j = 0; j < nb; ++j) {
+    const int64_t row0 = batch0 + j * stride + group;
+    if constexpr (TMA) {
+      const int s = static_cast<int>(j % STAGES);
+      const bool ok = ring.wait(s, static_cast<unsigned>(j / STAGES));
+      ring_tile<T, EPV, VPT, RB, RPC, CS, TPR, EXACT>(ring, s, 0, row0, group, lir, N, nvalid, tile);
+      // every thread has its copy of the stage: it can be refilled
+      if (__syncthreads_or(!ok) && !ring.dead) ring_give_up<decltype(ring), STAGES>(ring, a.status, j, nb);
+      if (tid == 0 && !ring.dead && j + STAGES < nb)
+        ring.issue(s, srcs, batch0 + (j + STAGES) * stride, N, D, crank);
+    } else if constexpr (PF == 0) {
       load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, row0, N, rowvecs, nvalid, tile);
+    }
 
     E xv[RB][VPT][NE];
-    float s[RB];
+    float s_[RB];
 #pragma unroll
     for (int r = 0; r < RB; ++r) {
       E acc = M::bcast(0.f);
@@ -167,16 +318,16 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
 #pragma unroll
         for (int e = 0; e < NE; ++e) acc = M::add(acc, xv[r][v][e]);
       }
-      s[r] = M::hsum(acc);
+      s_[r] = M::hsum(acc);
     }
-    if constexpr (PF)
+    if constexpr (PF == 1)
       load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, row0 + stride, N, rowvecs, nvalid, tile);
-    group_allreduce<RB, TPR, BLOCK, CS>(s, sm, phase, warp, lane);
+    group_allreduce<RB, TPR, BLOCK, CS>(s_, sm, phase, warp, lane);
 
     float mean[RB], q[RB];
 #pragma unroll
     for (int r = 0; r < RB; ++r) {
-      mean[r] = s[r] * inv_D;
+      mean[r] = s_[r] * inv_D;
       const E nm = M::bcast(-mean[r]);
       E acc = M::bcast(0.f);
 #pragma unroll
@@ -243,14 +394,18 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
 // ---------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------
-template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, bool PF,
+template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, int PF,
           bool EXACT, bool ROW_AFFINE>
 __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
     rows_bwd_kernel(const RowsArgs a) {
   constexpr int BLOCK = RowBlock<TPR>::kBlock;
   constexpr int RPC = RowBlock<TPR>::kRowsPerCta;
-  constexpr int VSTRIDE = TPR * CS;
+  constexpr bool TMA = PF >= 2;
+  constexpr int STAGES = TMA ? PF : 1;
+  using Map = VecMap<TPR, VPT, CS, TMA>;
+  constexpr int VSTRIDE = Map::kStride;
   static_assert(CS == 1 || RPC == 1, "cluster kernels own one row per cluster");
+  static_assert(!(TMA && CS > 1) || EXACT, "cluster slices need rows that fill the shape");
   constexpr bool PARAMS_IN_REGS = !ROW_AFFINE && PR;
   constexpr int CAP = TPR * VPT * EPV;  // columns one row group covers (CS == 1)
   using M = typename MathSel<EPV>::M;
@@ -258,6 +413,8 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
   constexpr int NE = MathSel<EPV>::NE;
   using P = Pack<T, EPV>;
 
+  extern __shared__ __align__(128) unsigned char ring_mem[];
+  __shared__ __align__(8) uint64_t ring_bars[STAGES];
   __shared__ ReduceSmem<2 * RB, BLOCK> sm;
   __shared__ float comb[(!ROW_AFFINE && RPC > 1) ? 2 * CAP : 1];
   int phase = 0;
@@ -275,7 +432,7 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
   const int64_t D = a.D;
   const int64_t rowvecs = D / EPV;
   const float inv_D = 1.0f / static_cast<float>(D);
-  const int vec0 = static_cast<int>(crank) * TPR + lir;
+  const int vec0 = Map::first(crank, lir);
   int nvalid = VPT;
   if constexpr (!EXACT) {
     const int left = static_cast<int>(rowvecs) - vec0;
@@ -307,14 +464,32 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
   }
 
   const int64_t stride = nunits * (RPC * RB);
-  const int64_t first = unit * (RPC * RB) + group;
+  const int64_t batch0 = unit * (RPC * RB);
+  const int64_t nb = batch0 < N ? (N - batch0 + stride - 1) / stride : 0;
   RowTile<T, EPV, VPT, RB> tx, tdy;
-  if constexpr (PF) {
-    load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, first, N, rowvecs, nvalid, tx);
-    load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(dyp, first, N, rowvecs, nvalid, tdy);
+  RowRing<T, EPV, VPT, RB, RPC, CS, STAGES, 2> ring;
+  const T* const srcs[2] = {static_cast<const T*>(a.x), static_cast<const T*>(a.dy)};
+  if constexpr (TMA) {
+    ring.init(ring_mem, ring_bars, D);
+    if (tid == 0) {
+      for (int64_t k = 0; k < STAGES && k < nb; ++k)
+        ring.issue(static_cast<int>(k), srcs, batch0 + k * stride, N, D, crank);
+    }
+  } else if constexpr (PF == 1) {
+    load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, batch0 + group, N, rowvecs, nvalid, tx);
+    load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(dyp, batch0 + group, N, rowvecs, nvalid, tdy);
   }
-  for (int64_t row0 = first; row0 - group < N; row0 += stride) {
-    if constexpr (!PF) {
+  for (int64_t j = 0; j < nb; ++j) {
+    const int64_t row0 = batch0 + j * stride + group;
+    if constexpr (TMA) {
+      const int s = static_cast<int>(j % STAGES);
+      const bool ok = ring.wait(s, static_cast<unsigned>(j / STAGES));
+      ring_tile<T, EPV, VPT, RB, RPC, CS, TPR, EXACT>(ring, s, 0, row0, group, lir, N, nvalid, tx);
+      ring_tile<T, EPV, VPT, RB, RPC, CS, TPR, EXACT>(ring, s, 1, row0, group, lir, N, nvalid, tdy);
+      if (__syncthreads_or(!ok) && !ring.dead) ring_give_up<decltype(ring), STAGES>(ring, a.status, j, nb);
+      if (tid == 0 && !ring.dead && j + STAGES < nb)
+        ring.issue(s, srcs, batch0 + (j + STAGES) * stride, N, D, crank);
+    } else if constexpr (PF == 0) {
       load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, row0, N, rowvecs, nvalid, tx);
       load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(dyp, row0, N, rowvecs, nvalid, tdy);
     }
@@ -359,7 +534,7 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
       red[2 * r] = M::hsum(r0);
       red[2 * r + 1] = M::hsum(r1);
     }
-    if constexpr (PF) {
+    if constexpr (PF == 1) {
       load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, row0 + stride, N, rowvecs, nvalid, tx);
       load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(dyp, row0 + stride, N, rowvecs, nvalid, tdy);
     }
@@ -464,12 +639,13 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
 // host-side launcher for one (T, EPV, affine, direction) family
 // ---------------------------------------------------------------------------
 template <typename Kernel>
-inline int resident_units(Kernel kernel, int block, int cs) {
+inline int resident_units(Kernel kernel, int block, int cs, size_t dyn_smem) {
   // Number of CTAs (CS == 1) or clusters that fit on the current device at once.
   int sms = device_sm_count();
   if (cs == 1) {
     int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, block, 0) != cudaSuccess ||
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, block, dyn_smem) !=
+            cudaSuccess ||
         per_sm < 1)
       per_sm = 1;
     return sms * per_sm;
@@ -477,6 +653,7 @@ inline int resident_units(Kernel kernel, int block, int cs) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(sms * cs), 1, 1);
   cfg.blockDim = dim3(static_cast<unsigned>(block), 1, 1);
+  cfg.dynamicSmemBytes = dyn_smem;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = static_cast<unsigned>(cs);
@@ -492,33 +669,66 @@ inline int resident_units(Kernel kernel, int block, int cs) {
   return clusters;
 }
 
-template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, bool PF,
+// Largest ring a TMA-mode kernel may ask for; wider problems use register prefetch.
+constexpr size_t kMaxRingBytes = 96 * 1024;
+
+template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, int PF,
           bool EXACT, bool ROW_AFFINE, bool BWD>
 inline cudaError_t launch_rows_exact(const RowsArgs& a, cudaStream_t stream, bool dry_run,
                                      RowsPlan* plan) {
   constexpr int BLOCK = RowBlock<TPR>::kBlock;
   constexpr int RPC = RowBlock<TPR>::kRowsPerCta;
+  constexpr bool TMA = PF >= 2;
+  size_t ring = 0;
+  if constexpr (TMA) {
+    const size_t row_bytes = static_cast<size_t>(a.D / CS) * sizeof(T);
+    ring = row_bytes * (CS == 1 ? RPC * RB : RB) * (BWD ? 2 : 1) * PF;
+    // rows that would need too large a ring, or clusters on rows that do not fill the
+    // shape, fall back to the register-prefetch twin of this shape
+    if (ring > kMaxRingBytes || (CS > 1 && !EXACT))
+      return launch_rows_exact<T, EPV, TPR, VPT, CS, RB, PR, MINB, 1, EXACT, ROW_AFFINE, BWD>(
+          a, stream, dry_run, plan);
+  }
   void (*kernel)(const RowsArgs);
   if constexpr (BWD) {
-    kernel = rows_bwd_kernel<T, EPV, TPR, VPT, CS, RB, PR, MINB, PF, EXACT, ROW_AFFINE>;
+    kernel = rows_bwd_kernel<T, EPV, TPR, VPT, CS, RB, PR, MINB, PF, (EXACT || (TMA && CS > 1)),
+                             ROW_AFFINE>;
   } else {
-    kernel = rows_fwd_kernel<T, EPV, TPR, VPT, CS, RB, PR, MINB, PF, EXACT, ROW_AFFINE>;
+    kernel = rows_fwd_kernel<T, EPV, TPR, VPT, CS, RB, PR, MINB, PF, (EXACT || (TMA && CS > 1)),
+                             ROW_AFFINE>;
   }
-  // Cached per process: every device this library runs on is the same part.
-  static std::atomic<int> cached_units{0};
-  int units = cached_units.load(std::memory_order_relaxed);
-  if (units == 0) {
+  // Cached per process: every device this library runs on is the same part.  The
+  // occupancy depends on the ring size, which depends on D.
+  static std::atomic<int64_t> cached{0};  // (ring bytes << 20) | units
+  static std::atomic<int> prepared{0};
+  if (prepared.load(std::memory_order_acquire) == 0) {
     if (CS > 8) {
       cudaError_t e =
           cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
       if (e != cudaSuccess) return e;
     }
-    units = resident_units(kernel, BLOCK, CS);
-    cached_units.store(units, std::memory_order_relaxed);
+    if (TMA) {
+      // the ring shares the SM's 227 KB with the kernel's static shared memory
+      cudaFuncAttributes fa;
+      cudaError_t e = cudaFuncGetAttributes(&fa, kernel);
+      if (e != cudaSuccess) return e;
+      const size_t room = 227 * 1024 - fa.sharedSizeBytes - 1024;
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kMaxRingBytes < room ? kMaxRingBytes : room));
+      if (e != cudaSuccess) return e;
+    }
+    prepared.store(1, std::memory_order_release);
+  }
+  int units = 0;
+  const int64_t c = cached.load(std::memory_order_relaxed);
+  if (c != 0 && static_cast<size_t>(c >> 20) == ring) {
+    units = static_cast<int>(c & 0xfffff);
+  } else {
+    units = resident_units(kernel, BLOCK, CS, ring);
+    cached.store((static_cast<int64_t>(ring) << 20) | units, std::memory_order_relaxed);
   }
   const int64_t need = (a.N + RPC * RB - 1) / (RPC * RB);
   int64_t use = need < units ? need : units;
-  if (!BWD && getenv("NVN_ONESHOT") != nullptr && need < 0x7fffffff / CS) use = need;
   plan->grid = static_cast<int>(use) * CS;
   plan->block = BLOCK;
   plan->cluster = CS;
@@ -526,13 +736,14 @@ inline cudaError_t launch_rows_exact(const RowsArgs& a, cudaStream_t stream, boo
   plan->vpt = VPT;
   plan->epv = EPV;
   plan->rb = RB;
+  plan->load_mode = PF;
   plan->partial_rows = static_cast<int>(use);
   if (dry_run) return cudaSuccess;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(plan->grid), 1, 1);
   cfg.blockDim = dim3(BLOCK, 1, 1);
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = ring;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   if (CS > 1) {
@@ -547,7 +758,7 @@ inline cudaError_t launch_rows_exact(const RowsArgs& a, cudaStream_t stream, boo
   return cudaLaunchKernelEx(&cfg, kernel, a);
 }
 
-template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, bool PF,
+template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, int PF,
           bool ROW_AFFINE, bool BWD>
 inline cudaError_t launch_rows_one(const RowsArgs& a, cudaStream_t stream, bool dry_run,
                                    RowsPlan* plan) {
@@ -567,7 +778,7 @@ cudaError_t launch_rows_vec(int shape, const RowsArgs& a, cudaStream_t s, bool d
   constexpr int EPV = VecTraits<T>::kFull;
 #define X(I, TPR, VPT, CS, RB, PR, MINB, PF) \
   case I:                                    \
-    return launch_rows_one<T, EPV, TPR, VPT, CS, RB, PR != 0, MINB, PF != 0, ROW_AFFINE, BWD>( \
+    return launch_rows_one<T, EPV, TPR, VPT, CS, RB, PR != 0, MINB, PF, ROW_AFFINE, BWD>( \
         a, s, dry, p);
   if constexpr (BWD && !ROW_AFFINE) {
     switch (shape) {
@@ -591,7 +802,7 @@ cudaError_t launch_rows_scalar(int shape, const RowsArgs& a, cudaStream_t s, boo
   switch (shape) {
 #define X(I, TPR, VPT, CS, RB, PR, MINB, PF) \
   case I:                                    \
-    return launch_rows_one<T, 1, TPR, VPT, CS, RB, PR != 0, MINB, PF != 0, ROW_AFFINE, BWD>( \
+    return launch_rows_one<T, 1, TPR, VPT, CS, RB, PR != 0, MINB, PF, ROW_AFFINE, BWD>( \
         a, s, dry, p);
     NVN_ROW_SHAPES_SCALAR(X)
 #undef X

@@ -190,10 +190,24 @@ def fused_layer_norm_op(x, scale, offset, axis: Iterable[int] = (-1,), epsilon: 
     return y, mean, inv_std
 
 
+def _grad_outputs(scale: torch.Tensor, out_grads):
+    """dgamma / dbeta buffers: fresh, or the caller's pair (e.g. two halves of one all-reduce
+    buffer).  Caller buffers must be contiguous float32 of scale's size on scale's device."""
+    if out_grads is None:
+        return torch.empty_like(scale), torch.empty_like(scale)
+    dgamma, dbeta = out_grads
+    for t in (dgamma, dbeta):
+        if (t.dtype != torch.float32 or t.numel() != scale.numel() or not t.is_contiguous()
+                or t.device != scale.device):
+            raise ValueError("out_grads must be two contiguous float32 tensors of scale's size")
+    return dgamma, dbeta
+
+
 def fused_layer_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_space_2,
-                             axis: Iterable[int] = (-1,), epsilon: float = 0.001):
+                             axis: Iterable[int] = (-1,), epsilon: float = 0.001, out_grads=None):
     """FusedLayerNormGrad (norm_ops.cc:161-174): returns (x_backprop, scale_backprop,
-    offset_backprop); the parameter gradients take the shape of `scale`."""
+    offset_backprop); the parameter gradients take the shape of `scale`.  `out_grads`
+    optionally supplies the (scale_backprop, offset_backprop) buffers."""
     _require(isinstance(y_backprop, torch.Tensor) and y_backprop.dim() > 0,
              "input must be at least 1-dimensional", _shape_str(y_backprop))
     _require(isinstance(x, torch.Tensor) and x.dim() > 0, "input must be at least 1-dimensional",
@@ -218,8 +232,7 @@ def fused_layer_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_spac
     x, dy, scale, mean, inv_std = _on_device((x, "x"), (dy, "y_backprop"), (scale, "scale"),
                                              (mean, "reserve_space_1"), (inv_std, "reserve_space_2"))
     dx = torch.empty_like(x)
-    dgamma = torch.empty_like(scale)
-    dbeta = torch.empty_like(scale)
+    dgamma, dbeta = _grad_outputs(scale, out_grads)
     with torch.cuda.device(x.device):
         lib = _lib.load()
         ws_ptr, ws_bytes = _workspace(x.device, lib.nvn_ln_bwd_workspace_bytes(code, N, D))
@@ -264,9 +277,9 @@ def fused_instance_norm_op(x, scale, offset, data_format: str = "N...C", epsilon
 
 
 def fused_instance_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_space_2,
-                                data_format: str = "N...C", epsilon: float = 0.001):
+                                data_format: str = "N...C", epsilon: float = 0.001, out_grads=None):
     """FusedInstanceNormGrad (norm_ops.cc:189-202): returns (x_backprop, scale_backprop,
-    offset_backprop)."""
+    offset_backprop).  `out_grads` optionally supplies the two parameter-gradient buffers."""
     _require(isinstance(y_backprop, torch.Tensor) and y_backprop.dim() > 3,
              "input must be at least 4-dimensional", _shape_str(y_backprop))
     _require(isinstance(x, torch.Tensor) and x.dim() > 1, "input must be at least 2-dimensional",
@@ -292,8 +305,7 @@ def fused_instance_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_s
     x, dy, scale, mean, inv_std = _on_device((x, "x"), (dy, "y_backprop"), (scale, "scale"),
                                              (mean, "reserve_space_1"), (inv_std, "reserve_space_2"))
     dx = torch.empty_like(x)
-    dgamma = torch.empty_like(scale)
-    dbeta = torch.empty_like(scale)
+    dgamma, dbeta = _grad_outputs(scale, out_grads)
     with torch.cuda.device(x.device):
         lib = _lib.load()
         ws_ptr, ws_bytes = _workspace(x.device, lib.nvn_in_bwd_workspace_bytes(code, N, C, D, int(cf)))

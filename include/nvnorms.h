@@ -66,7 +66,8 @@ typedef enum nvn_status {
   NVN_ERR_WORKSPACE = -6,        /* workspace missing, misaligned or too small         */
   NVN_ERR_CUDA = -7,             /* a CUDA runtime call failed (see nvn_last_cuda_error) */
   NVN_ERR_UNSUPPORTED = -8,      /* size beyond what the kernels index                 */
-  NVN_ERR_LIMIT = -9             /* size beyond a fixed built-in capacity              */
+  NVN_ERR_LIMIT = -9,            /* size beyond a fixed built-in capacity              */
+  NVN_ERR_TIMEOUT = -10          /* a kernel gave up a bounded wait (see nvn_device_status) */
 } nvn_status;
 
 /* Library version: major*10000 + minor*100 + patch. */
@@ -78,6 +79,13 @@ NVN_API const char* nvn_status_string(int status);
 
 /* cudaError_t value of the most recent failing CUDA call on this thread (0 if none). */
 NVN_API int nvn_last_cuda_error(void);
+
+/* Diagnostic: synchronises with the current device and reports whether any kernel of this
+ * library has given up a bounded wait on an asynchronous copy since the process started
+ * (NVN_OK, NVN_ERR_TIMEOUT, or NVN_ERR_CUDA).  Every wait inside the kernels has an
+ * iteration limit, so a logic error surfaces here instead of as a hung GPU.  The reference
+ * has no counterpart (its kernels do not wait on anything). */
+NVN_API int nvn_device_status(void);
 
 /* Number of kernel launches this library has issued in this process so far. */
 NVN_API uint64_t nvn_launch_count(void);

@@ -16,6 +16,9 @@
  * uint16_t bit patterns).  gamma, beta and the saved statistics are fp32.
  */
 #include <math.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -133,6 +136,18 @@ static inline void store_elem_t(int dtype, void* p, int64_t i, float v) {
 #undef SUFFIX
 #undef SQRT
 #undef STORE_OUT
+
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; a timed baseline that is meant to use
+ * every host core sets the team size explicitly.  Returns the team size now in effect. */
+int oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
 
 /* exposed for the oracle's own unit tests */
 float oracle_half_to_f32(uint16_t h) { return half_to_f32(h); }

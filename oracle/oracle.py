@@ -44,6 +44,14 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+def set_num_threads(n: int) -> int:
+    """Size of the OpenMP team used by the C oracle from now on; returns what is in effect."""
+    fn = lib().oracle_set_num_threads
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int]
+    return int(fn(int(n)))
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
 
