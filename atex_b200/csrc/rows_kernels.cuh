@@ -151,16 +151,14 @@ struct RowRing {
     return mbar_wait_bounded(&full[s], use & 1u);
   }
 
-  // Vector v of row-slot r of tensor t for this thread; `slot_vec` is the thread's first
-  // vector inside a row (slice) and consecutive vectors of a thread are VSTRIDE apart.
-  template <int VSTRIDE>
-  __device__ __forceinline__ Pack<T, EPV> read(int s, int t, int rowslot, int slot_vec,
-                                               int v) const {
-    const unsigned char* p = base + static_cast<size_t>(s) * stage_bytes + t * tensor_bytes +
-                             static_cast<size_t>(rowslot) * row_bytes;
-    return *reinterpret_cast<const Pack<T, EPV>*>(p + (static_cast<size_t>(slot_vec) +
-                                                       static_cast<size_t>(v) * VSTRIDE) *
-                                                          sizeof(Pack<T, EPV>));
+  // Byte offset, inside a stage, of this thread's first vector of row-slot `rowslot` of
+  // tensor t.  Computed once per thread; the per-vector offsets are compile-time constants.
+  __device__ __forceinline__ unsigned thread_offset(int t, int rowslot, int slot_vec) const {
+    return t * tensor_bytes + rowslot * row_bytes +
+           static_cast<unsigned>(slot_vec) * static_cast<unsigned>(sizeof(Pack<T, EPV>));
+  }
+  __device__ __forceinline__ const unsigned char* stage_ptr(int s) const {
+    return base + static_cast<size_t>(s) * stage_bytes;
   }
 };
 
@@ -178,19 +176,20 @@ struct VecMap {
   }
 };
 
-// Tile of the current row batch out of ring stage `s` (TMA mode).
-template <typename T, int EPV, int VPT, int RB, int RPC, int CS, int TPR, bool EXACT, typename Ring>
-__device__ __forceinline__ void ring_tile(const Ring& ring, int s, int t, int64_t row_first,
-                                          int group, int lir, int64_t N, int nvalid,
+// Tile of the current row batch out of a ring stage (TMA mode).  `off[r]` are the thread's
+// precomputed byte offsets (RowRing::thread_offset) of its RB row slots.
+template <typename T, int EPV, int VPT, int RB, int RPC, int TPR, bool EXACT>
+__device__ __forceinline__ void ring_tile(const unsigned char* stage, const unsigned (&off)[RB],
+                                          int64_t row_first, int64_t N, int nvalid,
                                           RowTile<T, EPV, VPT, RB>& tile) {
 #pragma unroll
   for (int r = 0; r < RB; ++r) {
     const bool rv = row_first + r * RPC < N;
-    const int slot = CS == 1 ? r * RPC + group : r;
+    const Pack<T, EPV>* p = reinterpret_cast<const Pack<T, EPV>*>(stage + off[r]);
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       if (rv && (EXACT || v < nvalid)) {
-        tile.p[r][v] = ring.template read<TPR>(s, t, slot, lir, v);
+        tile.p[r][v] = p[v * TPR];
       } else {
 #pragma unroll
         for (int e = 0; e < EPV; ++e) tile.p[r][v].v[e] = Cvt<T>::from_f32(0.f);
@@ -284,8 +283,12 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
   RowTile<T, EPV, VPT, RB> tile;
   RowRing<T, EPV, VPT, RB, RPC, CS, STAGES, 1> ring;
   const T* const srcs[1] = {static_cast<const T*>(a.x)};
+  unsigned roff[RB];
   if constexpr (TMA) {
     ring.init(ring_mem, ring_bars, D);
+#pragma unroll
+    for (int r = 0; r < RB; ++r)
+      roff[r] = ring.thread_offset(0, CS == 1 ? r * RPC + group : r, lir);
     if (tid == 0) {
       for (int64_t k = 0; k < STAGES && k < nb; ++k)
         ring.issue(static_cast<int>(k), srcs, batch0 + k * stride, N, D, crank);
@@ -298,7 +301,7 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
     if constexpr (TMA) {
       const int s = static_cast<int>(j % STAGES);
       const bool ok = ring.wait(s, static_cast<unsigned>(j / STAGES));
-      ring_tile<T, EPV, VPT, RB, RPC, CS, TPR, EXACT>(ring, s, 0, row0, group, lir, N, nvalid, tile);
+      ring_tile<T, EPV, VPT, RB, RPC, TPR, EXACT>(ring.stage_ptr(s), roff, row0, N, nvalid, tile);
       // every thread has its copy of the stage: it can be refilled
       if (__syncthreads_or(!ok) && !ring.dead) ring_give_up<decltype(ring), STAGES>(ring, a.status, j, nb);
       if (tid == 0 && !ring.dead && j + STAGES < nb)
@@ -469,8 +472,14 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
   RowTile<T, EPV, VPT, RB> tx, tdy;
   RowRing<T, EPV, VPT, RB, RPC, CS, STAGES, 2> ring;
   const T* const srcs[2] = {static_cast<const T*>(a.x), static_cast<const T*>(a.dy)};
+  unsigned xoff[RB], dyoff[RB];
   if constexpr (TMA) {
     ring.init(ring_mem, ring_bars, D);
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      xoff[r] = ring.thread_offset(0, CS == 1 ? r * RPC + group : r, lir);
+      dyoff[r] = ring.thread_offset(1, CS == 1 ? r * RPC + group : r, lir);
+    }
     if (tid == 0) {
       for (int64_t k = 0; k < STAGES && k < nb; ++k)
         ring.issue(static_cast<int>(k), srcs, batch0 + k * stride, N, D, crank);
@@ -479,13 +488,27 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
     load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, batch0 + group, N, rowvecs, nvalid, tx);
     load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(dyp, batch0 + group, N, rowvecs, nvalid, tdy);
   }
+  // The saved statistics of a row are needed the moment its data arrives; fetched on demand
+  // they would expose a full memory latency per row batch, so they run two batches ahead.
+  float st_mean[3][RB], st_ivar[3][RB];
+  auto load_stats = [&](int slot, int64_t first_row) {
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      const int64_t row = first_row + r * RPC;
+      const bool rv = row < N;
+      st_mean[slot][r] = rv ? __ldg(a.mean_in + row) : 0.f;
+      st_ivar[slot][r] = rv ? __ldg(a.ivar_in + row) : 0.f;
+    }
+  };
+  load_stats(0, batch0 + group);
+  load_stats(1, batch0 + stride + group);
   for (int64_t j = 0; j < nb; ++j) {
     const int64_t row0 = batch0 + j * stride + group;
     if constexpr (TMA) {
       const int s = static_cast<int>(j % STAGES);
       const bool ok = ring.wait(s, static_cast<unsigned>(j / STAGES));
-      ring_tile<T, EPV, VPT, RB, RPC, CS, TPR, EXACT>(ring, s, 0, row0, group, lir, N, nvalid, tx);
-      ring_tile<T, EPV, VPT, RB, RPC, CS, TPR, EXACT>(ring, s, 1, row0, group, lir, N, nvalid, tdy);
+      ring_tile<T, EPV, VPT, RB, RPC, TPR, EXACT>(ring.stage_ptr(s), xoff, row0, N, nvalid, tx);
+      ring_tile<T, EPV, VPT, RB, RPC, TPR, EXACT>(ring.stage_ptr(s), dyoff, row0, N, nvalid, tdy);
       if (__syncthreads_or(!ok) && !ring.dead) ring_give_up<decltype(ring), STAGES>(ring, a.status, j, nb);
       if (tid == 0 && !ring.dead && j + STAGES < nb)
         ring.issue(s, srcs, batch0 + (j + STAGES) * stride, N, D, crank);
@@ -494,16 +517,15 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
       load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(dyp, row0, N, rowvecs, nvalid, tdy);
     }
     float ivar[RB];
+    load_stats(2, row0 + 2 * stride);
     // xh = (x - mean) * ivar ; gy = dy * gamma (LayerNorm) or dy (row-affine, where
     // gamma is a per-row scalar applied at the end).  red = (sum gy, sum gy * xh).
     E xh[RB][VPT][NE], gy[RB][VPT][NE];
     float red[2 * RB];
 #pragma unroll
     for (int r = 0; r < RB; ++r) {
-      const int64_t row = row0 + r * RPC;
-      const bool rv = row < N;
-      const float mean = rv ? __ldg(a.mean_in + row) : 0.f;
-      ivar[r] = rv ? __ldg(a.ivar_in + row) : 0.f;
+      const float mean = st_mean[0][r];
+      ivar[r] = st_ivar[0][r];
       const E nm = M::bcast(-mean), iv2 = M::bcast(ivar[r]);
       E r0 = M::bcast(0.f), r1 = M::bcast(0.f);
 #pragma unroll
@@ -533,6 +555,13 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
       }
       red[2 * r] = M::hsum(r0);
       red[2 * r + 1] = M::hsum(r1);
+    }
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      st_mean[0][r] = st_mean[1][r];
+      st_ivar[0][r] = st_ivar[1][r];
+      st_mean[1][r] = st_mean[2][r];
+      st_ivar[1][r] = st_ivar[2][r];
     }
     if constexpr (PF == 1) {
       load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, row0 + stride, N, rowvecs, nvalid, tx);

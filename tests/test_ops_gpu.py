@@ -313,3 +313,15 @@ def test_mixed_precision_layer_keeps_fp32_weights():
     inn = A.InstanceNormalization(axis=-1)
     y = inn(xi)
     assert y.dtype == torch.float16 and inn.gamma.dtype == torch.float32
+
+
+def test_tma_ring_path_is_used_and_no_bounded_wait_ever_gave_up(lib):
+    """The benchmark shape runs its forward through the cp.async.bulk ring; its waits are
+    bounded and report through the device status word, which must still be clean after
+    everything this process has launched so far."""
+    plan = _lib.describe_plan(0, _lib.NVN_BF16, 32768, 1, 4096, 0)
+    assert "load=tma" in plan, plan
+    for (N, D, dtype) in [(3001, 4096, "bf16"), (70000, 128, "f16"), (513, 1024, "f32"), (37, 3072, "bf16")]:
+        x, dy, g, b = rand_ln(N, D, dtype, seed=N)
+        check_ln(x, dy, g, b, 1e-5)
+    assert lib.nvn_device_status() == _lib.NVN_OK
