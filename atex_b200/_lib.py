@@ -32,6 +32,16 @@ _vp = _c.c_void_p
 _int = _c.c_int
 _sz = _c.c_size_t
 
+NVN_DP_MAX_RANKS = 16
+
+
+class DpComm(ctypes.Structure):
+    """nvn_dp_comm of include/nvnorms.h."""
+    _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int),
+                ("recv", ctypes.c_void_p * NVN_DP_MAX_RANKS),
+                ("epoch", ctypes.c_uint32), ("defer", ctypes.c_int)]
+
+
 # name -> (restype, argtypes); mirrors include/nvnorms.h declaration by declaration
 SIGNATURES = {
     "nvn_version": (_int, []),
@@ -54,6 +64,12 @@ SIGNATURES = {
     "nvn_in_bwd": (_int, [_int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp,
                           _vp, _sz, _vp]),
     "nvn_describe_plan": (_int, [_int, _int, _i64, _i64, _i64, _int, _c.c_char_p, _sz]),
+    "nvn_dp_finish": (_int, [_i64, _c.POINTER(DpComm), _vp, _vp, _vp]),
+    "nvn_dp_recv_bytes": (_sz, [_i64, _int]),
+    "nvn_ln_bwd_dp": (_int, [_int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _sz,
+                             _c.POINTER(DpComm), _vp]),
+    "nvn_in_bwd_dp": (_int, [_int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp,
+                             _vp, _sz, _c.POINTER(DpComm), _vp]),
 }
 
 _lib = None

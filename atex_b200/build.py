@@ -42,6 +42,7 @@ def _units():
             units.append((f"rows_{tname}_{dname}.o", "rows_inst.cu", [f"-DNVN_T={t}", f"-DNVN_BWD={b}"]))
     units.append(("twophase.o", "twophase.cu", []))
     units.append(("colreduce.o", "colreduce.cu", []))
+    units.append(("colreduce_dp.o", "colreduce_dp.cu", []))
     units.append(("nvnorms_api.o", "nvnorms_api.cu", []))
     extra = os.path.join(CSRC, "noalloc.cu")
     if os.path.exists(extra):

@@ -1,0 +1,184 @@
+// Column reduction fused with the data-parallel all-reduce of [dgamma | dbeta].
+//
+// In a data-parallel job every rank (one process, one GPU) ends its backward pass with
+// P partial rows of [2][F] floats.  nvn::colreduce sums them locally; the ranks then
+// still have to add their vectors up.  That exchange is a few KB, so it is pure
+// latency.  This kernel does both steps in one launch over NVLink peer memory:
+//
+//   1. every CTA sums its 128 columns over the P local partial rows (same fixed order
+//      as colreduce_kernel);
+//   2. it stores that slice into the receive buffer of EVERY rank with plain 8-byte peer
+//      stores, each carrying one value and the epoch number (slot = epoch mod 4, row = own
+//      rank).  An aligned 8-byte store arrives as a whole, so the epoch next to a value
+//      says the value is there: no fence and no separate flag, one NVLink traversal;
+//   3. it polls - BOUNDED - the `world` rows of its own receive buffer until every element
+//      carries this epoch and adds the values in rank order.
+//
+// Every rank adds the same numbers in the same order, so dgamma / dbeta are
+// bit-identical on all ranks and from run to run.  Each CTA pushes before it polls and
+// only waits for CTAs of other GPUs, so no CTA waits for one that cannot be scheduled.
+// Four receive slots (epoch mod 4): with a single fused launch a rank can only get one
+// epoch ahead of the slowest rank (finishing epoch e needs every rank's push of e); in
+// the deferred form (push now, finish later on another stream) the caller keeps the push
+// of epoch e+1 behind its own finish of epoch e-2, which keeps every slot's readers done
+// before it is overwritten.  A poll that exceeds its limit raises the device status word
+// and the kernel finishes with whatever arrived; it never hangs.  No multimem and no
+// multicast instruction is used: plain st / ld.
+//
+// The reference has no communication at all (its ops are single-device); this stands
+// where a data-parallel TensorFlow job would run an all-reduce after the op.
+#include "../../include/nvnorms.h"
+#include "nvn_host.h"
+
+namespace nvn {
+
+namespace {
+constexpr int kTX = 32;
+constexpr int kW = 4;            // columns per thread
+constexpr unsigned kPollLimit = 1u << 22;
+
+struct DpPtrs {
+  uint2* recv[NVN_DP_MAX_RANKS];  // (value bits, epoch) pairs
+  int rank, world;
+  unsigned epoch;
+  int* status;
+};
+
+__device__ __forceinline__ void st_pair(uint2* p, float v, unsigned epoch) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)),
+               "r"(epoch)
+               : "memory");
+}
+__device__ __forceinline__ uint2 ld_pair(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
+// PUSH: steps 1 and 2.  FINISH: step 3.  <true, true> is the single fused launch;
+// <true, false> followed later (possibly on another stream) by <false, true> lets the
+// caller overlap the wait with other work.
+template <int TY, bool PUSH, bool FINISH>
+__global__ void __launch_bounds__(kTX* TY)
+    colreduce_allreduce_kernel(const float* __restrict__ partials, int64_t P, int64_t F,
+                               const DpPtrs c, float* __restrict__ dgamma,
+                               float* __restrict__ dbeta) {
+  __shared__ float tile[TY][kTX * kW + 1];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int64_t F2 = 2 * F;
+  const int64_t col = (static_cast<int64_t>(blockIdx.x) * kTX + tx) * kW;
+  const int64_t slot = static_cast<int64_t>(c.epoch & 3u) * c.world;
+  if constexpr (PUSH) {
+  float s[kW] = {0.f, 0.f, 0.f, 0.f};
+  if (col < F2) {
+    for (int64_t p = ty; p < P; p += TY) {
+      const float4 v = *reinterpret_cast<const float4*>(partials + p * F2 + col);
+      s[0] += v.x;
+      s[1] += v.y;
+      s[2] += v.z;
+      s[3] += v.w;
+    }
+  }
+#pragma unroll
+  for (int w = 0; w < kW; ++w) tile[ty][tx * kW + w] = s[w];
+  __syncthreads();
+  if (ty == 0 && col < F2) {
+    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < TY; ++k) {
+      t.x += tile[k][tx * kW + 0];
+      t.y += tile[k][tx * kW + 1];
+      t.z += tile[k][tx * kW + 2];
+      t.w += tile[k][tx * kW + 3];
+    }
+    const float o[kW] = {t.x, t.y, t.z, t.w};
+    for (int p = 0; p < c.world; ++p) {
+      uint2* dst = c.recv[p] + (slot + c.rank) * F2 + col;
+#pragma unroll
+      for (int w = 0; w < kW; ++w) st_pair(dst + w, o[w], c.epoch);
+    }
+  }
+  }  // PUSH
+  if constexpr (!FINISH) return;
+  // bounded poll of this rank's own receive rows, then the sum in rank order
+  int ok = 1;
+  float acc[kW] = {0.f, 0.f, 0.f, 0.f};
+  if (ty == 0 && col < F2) {
+    for (int r = 0; r < c.world; ++r) {
+      const uint2* src = c.recv[c.rank] + (slot + r) * F2 + col;
+#pragma unroll
+      for (int w = 0; w < kW; ++w) {
+        uint2 v = ld_pair(src + w);
+        unsigned polls = 0;
+        while (v.y != c.epoch) {
+          if (++polls > kPollLimit) {
+            ok = 0;
+            break;
+          }
+          v = ld_pair(src + w);
+        }
+        acc[w] += __uint_as_float(v.x);
+      }
+    }
+#pragma unroll
+    for (int w = 0; w < kW; ++w) {
+      const int64_t cc = col + w;
+      if (cc < F) {
+        dgamma[cc] = acc[w];
+      } else {
+        dbeta[cc - F] = acc[w];
+      }
+    }
+  }
+  if (!__syncthreads_and(ok)) {
+    if (tx == 0 && ty == 0 && c.status != nullptr) atomicExch(c.status, 1);
+  }
+}
+
+template <int TY, bool PUSH, bool FINISH>
+cudaError_t launch(const float* partials, int64_t P, int64_t F, const DpPtrs& c, float* dgamma,
+                   float* dbeta, cudaStream_t s) {
+  const int64_t blocks = (2 * F + kTX * kW - 1) / (kTX * kW);
+  count_launch();
+  colreduce_allreduce_kernel<TY, PUSH, FINISH><<<static_cast<unsigned>(blocks), dim3(kTX, TY), 0, s>>>(
+      partials, P, F, c, dgamma, dbeta);
+  return cudaGetLastError();
+}
+
+DpPtrs make_ptrs(const nvn_dp_comm* comm) {
+  DpPtrs c;
+  c.rank = comm->rank;
+  c.world = comm->world;
+  c.epoch = comm->epoch;
+  c.status = device_status_word();
+  for (int i = 0; i < NVN_DP_MAX_RANKS; ++i) {
+    c.recv[i] = i < comm->world ? static_cast<uint2*>(comm->recv[i]) : nullptr;
+  }
+  return c;
+}
+
+template <bool FINISH>
+cudaError_t launch_push(const float* partials, int64_t P, int64_t F, const DpPtrs& c,
+                        float* dgamma, float* dbeta, cudaStream_t s) {
+  if (P <= 4) return launch<1, true, FINISH>(partials, P, F, c, dgamma, dbeta, s);
+  if (P <= 32) return launch<4, true, FINISH>(partials, P, F, c, dgamma, dbeta, s);
+  if (P <= 128 || 2 * F >= 32768) return launch<8, true, FINISH>(partials, P, F, c, dgamma, dbeta, s);
+  return launch<32, true, FINISH>(partials, P, F, c, dgamma, dbeta, s);
+}
+}  // namespace
+
+cudaError_t colreduce_allreduce_launch(const float* partials, int64_t P, int64_t F,
+                                       const nvn_dp_comm* comm, float* dgamma, float* dbeta,
+                                       cudaStream_t s) {
+  const DpPtrs c = make_ptrs(comm);
+  // comm->defer: only reduce and push here; nvn_dp_finish completes the exchange later
+  return comm->defer ? launch_push<false>(partials, P, F, c, dgamma, dbeta, s)
+                     : launch_push<true>(partials, P, F, c, dgamma, dbeta, s);
+}
+
+cudaError_t dp_finish_launch(int64_t F, const nvn_dp_comm* comm, float* dgamma, float* dbeta,
+                             cudaStream_t s) {
+  return launch<1, false, true>(nullptr, 0, F, make_ptrs(comm), dgamma, dbeta, s);
+}
+
+}  // namespace nvn

@@ -6,6 +6,8 @@
 
 #include <atomic>
 
+struct nvn_dp_comm;
+
 namespace nvn {
 
 // Arguments of the row-cached kernels (rows_kernels.cuh).  `out` is y (forward)
@@ -98,6 +100,14 @@ NVN_DECLARE_ROWS(rows_bf16_bwd)
 // Deterministic second stage of the dgamma / dbeta reduction: sums P partial
 // rows of [2][F] floats (dgamma then dbeta) in a fixed order.
 cudaError_t colreduce_launch(const float* partials, int64_t P, int64_t F, float* dgamma,
+                             float* dbeta, cudaStream_t s);
+
+// Column reduction fused with the all-reduce over peer memory (colreduce_dp.cu).  Needs
+// 2F % 4 == 0.
+cudaError_t colreduce_allreduce_launch(const float* partials, int64_t P, int64_t F,
+                                       const struct ::nvn_dp_comm* comm, float* dgamma,
+                                       float* dbeta, cudaStream_t s);
+cudaError_t dp_finish_launch(int64_t F, const struct ::nvn_dp_comm* comm, float* dgamma,
                              float* dbeta, cudaStream_t s);
 
 }  // namespace nvn

@@ -168,7 +168,7 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
              const float* gamma, const float* beta, const float* mean_in, const float* ivar_in,
              int64_t rows, int64_t D, int64_t N, int64_t C, float eps, void* out, float* mean,
              float* ivar, float* dgamma, float* dbeta, void* ws, size_t ws_bytes,
-             cudaStream_t stream) {
+             cudaStream_t stream, const nvn_dp_comm* comm = nullptr) {
   bool vec_ok = aligned(x, 16) && aligned(out, 16) && aligned(gamma, 16);
   if (bwd) {
     vec_ok = vec_ok && aligned(dy, 16);
@@ -225,8 +225,11 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
     if (e != cudaSuccess) return fail_cuda(e);
   }
   if (bwd) {
-    cudaError_t e = colreduce_launch(reinterpret_cast<const float*>(wsb + p.off_colpart),
-                                     p.colpart_rows, F, dgamma, dbeta, stream);
+    const float* partials = reinterpret_cast<const float*>(wsb + p.off_colpart);
+    cudaError_t e = comm != nullptr ? colreduce_allreduce_launch(partials, p.colpart_rows, F, comm,
+                                                                 dgamma, dbeta, stream)
+                                    : colreduce_launch(partials, p.colpart_rows, F, dgamma, dbeta,
+                                                       stream);
     if (e != cudaSuccess) return fail_cuda(e);
   }
   return NVN_OK;
@@ -265,7 +268,8 @@ int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, 
 int run_nlc(int dtype, bool bwd, const void* dy, const void* x, const float* gamma,
             const float* beta, const float* mean_in, const float* ivar_in, int64_t N, int64_t C,
             int64_t D, float eps, void* out, float* mean, float* ivar, float* dgamma,
-            float* dbeta, void* ws, size_t ws_bytes, cudaStream_t stream) {
+            float* dbeta, void* ws, size_t ws_bytes, cudaStream_t stream,
+            const nvn_dp_comm* comm = nullptr) {
   bool vec_ok = aligned(x, 16) && aligned(out, 16) && (!bwd || aligned(dy, 16));
   NlcPlan p;
   int st = plan_nlc(dtype, bwd, N, C, D, vec_ok, &p);
@@ -290,7 +294,9 @@ int run_nlc(int dtype, bool bwd, const void* dy, const void* x, const float* gam
   cudaError_t e = s2_launch(dtype, bwd, p.scalar, a, p.s2, stream);
   if (e != cudaSuccess) return fail_cuda(e);
   if (bwd) {
-    e = colreduce_launch(a.ws_colpart, N, C, dgamma, dbeta, stream);
+    e = comm != nullptr
+            ? colreduce_allreduce_launch(a.ws_colpart, N, C, comm, dgamma, dbeta, stream)
+            : colreduce_launch(a.ws_colpart, N, C, dgamma, dbeta, stream);
     if (e != cudaSuccess) return fail_cuda(e);
   }
   return NVN_OK;
@@ -496,9 +502,10 @@ int nvn_ln_fwd(int dtype, const void* x, const float* gamma, const float* beta, 
                   static_cast<cudaStream_t>(stream));
 }
 
-int nvn_ln_bwd(int dtype, const void* dy, const void* x, const float* gamma, const float* mean,
-               const float* inv_std, int64_t N, int64_t D, void* dx, float* dgamma,
-               float* dbeta, void* workspace, size_t workspace_bytes, void* stream) {
+static int ln_bwd_impl(int dtype, const void* dy, const void* x, const float* gamma,
+                       const float* mean, const float* inv_std, int64_t N, int64_t D, void* dx,
+                       float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes,
+                       const nvn_dp_comm* comm, void* stream) {
   if (!valid_dtype(dtype) || N < 0 || D < 0) return NVN_ERR_INVALID_ARGUMENT;
   if (D > 0 && (dgamma == nullptr || dbeta == nullptr)) return NVN_ERR_INVALID_ARGUMENT;
   if (N == 0 || D == 0) return zero_grads(dgamma, dbeta, D, static_cast<cudaStream_t>(stream));
@@ -507,7 +514,52 @@ int nvn_ln_bwd(int dtype, const void* dy, const void* x, const float* gamma, con
     return NVN_ERR_INVALID_ARGUMENT;
   return run_rows(dtype, true, false, dy, x, gamma, nullptr, mean, inv_std, N, D, N, 1, 0.f, dx,
                   nullptr, nullptr, dgamma, dbeta, workspace, workspace_bytes,
-                  static_cast<cudaStream_t>(stream));
+                  static_cast<cudaStream_t>(stream), comm);
+}
+
+int nvn_ln_bwd(int dtype, const void* dy, const void* x, const float* gamma, const float* mean,
+               const float* inv_std, int64_t N, int64_t D, void* dx, float* dgamma,
+               float* dbeta, void* workspace, size_t workspace_bytes, void* stream) {
+  return ln_bwd_impl(dtype, dy, x, gamma, mean, inv_std, N, D, dx, dgamma, dbeta, workspace,
+                     workspace_bytes, nullptr, stream);
+}
+
+// Every rank must take part in the exchange, also with an empty local shard, so the
+// data-parallel variants reject empty problems instead of silently skipping the kernel.
+static int check_comm(const nvn_dp_comm* c, int64_t F) {
+  if (c == nullptr || c->world < 1 || c->world > NVN_DP_MAX_RANKS || c->rank < 0 ||
+      c->rank >= c->world || c->epoch == 0 || F % 2 != 0)
+    return NVN_ERR_INVALID_ARGUMENT;
+  for (int i = 0; i < c->world; ++i)
+    if (c->recv[i] == nullptr || !aligned(c->recv[i], 16))
+      return NVN_ERR_INVALID_ARGUMENT;
+  return NVN_OK;
+}
+
+int nvn_dp_finish(int64_t F, const nvn_dp_comm* comm, float* dgamma, float* dbeta,
+                  void* stream) {
+  if (F <= 0 || dgamma == nullptr || dbeta == nullptr) return NVN_ERR_INVALID_ARGUMENT;
+  const int st = check_comm(comm, F);
+  if (st != NVN_OK) return st;
+  cudaError_t e = dp_finish_launch(F, comm, dgamma, dbeta, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? NVN_OK : fail_cuda(e);
+}
+
+size_t nvn_dp_recv_bytes(int64_t F, int world) {
+  if (F <= 0 || world < 1) return 0;
+  // [4 slots][world][2F] pairs of (value, epoch)
+  return static_cast<size_t>(4) * world * 2 * F * 2 * sizeof(uint32_t);
+}
+
+int nvn_ln_bwd_dp(int dtype, const void* dy, const void* x, const float* gamma,
+                  const float* mean, const float* inv_std, int64_t N, int64_t D, void* dx,
+                  float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes,
+                  const nvn_dp_comm* comm, void* stream) {
+  if (N <= 0 || D <= 0) return NVN_ERR_INVALID_ARGUMENT;
+  const int st = check_comm(comm, D);
+  if (st != NVN_OK) return st;
+  return ln_bwd_impl(dtype, dy, x, gamma, mean, inv_std, N, D, dx, dgamma, dbeta, workspace,
+                     workspace_bytes, comm, stream);
 }
 
 int nvn_in_fwd(int dtype, const void* x, const float* gamma, const float* beta, int64_t N,
@@ -527,10 +579,10 @@ int nvn_in_fwd(int dtype, const void* x, const float* gamma, const float* beta, 
                  mean, inv_std, nullptr, nullptr, workspace, workspace_bytes, s);
 }
 
-int nvn_in_bwd(int dtype, const void* dy, const void* x, const float* gamma, const float* mean,
-               const float* inv_std, int64_t N, int64_t C, int64_t D, int channel_first,
-               void* dx, float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes,
-               void* stream) {
+static int in_bwd_impl(int dtype, const void* dy, const void* x, const float* gamma,
+                       const float* mean, const float* inv_std, int64_t N, int64_t C, int64_t D,
+                       int channel_first, void* dx, float* dgamma, float* dbeta, void* workspace,
+                       size_t workspace_bytes, const nvn_dp_comm* comm, void* stream) {
   if (!valid_dtype(dtype) || N < 0 || C < 0 || D < 0) return NVN_ERR_INVALID_ARGUMENT;
   if (C > 0 && (dgamma == nullptr || dbeta == nullptr)) return NVN_ERR_INVALID_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -540,9 +592,29 @@ int nvn_in_bwd(int dtype, const void* dy, const void* x, const float* gamma, con
     return NVN_ERR_INVALID_ARGUMENT;
   if (channel_first || C == 1)
     return run_rows(dtype, true, true, dy, x, gamma, nullptr, mean, inv_std, N * C, D, N, C,
-                    0.f, dx, nullptr, nullptr, dgamma, dbeta, workspace, workspace_bytes, s);
+                    0.f, dx, nullptr, nullptr, dgamma, dbeta, workspace, workspace_bytes, s,
+                    comm);
   return run_nlc(dtype, true, dy, x, gamma, nullptr, mean, inv_std, N, C, D, 0.f, dx, nullptr,
-                 nullptr, dgamma, dbeta, workspace, workspace_bytes, s);
+                 nullptr, dgamma, dbeta, workspace, workspace_bytes, s, comm);
+}
+
+int nvn_in_bwd(int dtype, const void* dy, const void* x, const float* gamma, const float* mean,
+               const float* inv_std, int64_t N, int64_t C, int64_t D, int channel_first,
+               void* dx, float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes,
+               void* stream) {
+  return in_bwd_impl(dtype, dy, x, gamma, mean, inv_std, N, C, D, channel_first, dx, dgamma,
+                     dbeta, workspace, workspace_bytes, nullptr, stream);
+}
+
+int nvn_in_bwd_dp(int dtype, const void* dy, const void* x, const float* gamma,
+                  const float* mean, const float* inv_std, int64_t N, int64_t C, int64_t D,
+                  int channel_first, void* dx, float* dgamma, float* dbeta, void* workspace,
+                  size_t workspace_bytes, const nvn_dp_comm* comm, void* stream) {
+  if (N <= 0 || C <= 0 || D <= 0) return NVN_ERR_INVALID_ARGUMENT;
+  const int st = check_comm(comm, C);
+  if (st != NVN_OK) return st;
+  return in_bwd_impl(dtype, dy, x, gamma, mean, inv_std, N, C, D, channel_first, dx, dgamma,
+                     dbeta, workspace, workspace_bytes, comm, stream);
 }
 
 int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int channel_first,

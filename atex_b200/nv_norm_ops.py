@@ -204,10 +204,13 @@ def _grad_outputs(scale: torch.Tensor, out_grads):
 
 
 def fused_layer_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_space_2,
-                             axis: Iterable[int] = (-1,), epsilon: float = 0.001, out_grads=None):
+                             axis: Iterable[int] = (-1,), epsilon: float = 0.001, out_grads=None,
+                             grad_exchange=None):
     """FusedLayerNormGrad (norm_ops.cc:161-174): returns (x_backprop, scale_backprop,
     offset_backprop); the parameter gradients take the shape of `scale`.  `out_grads`
-    optionally supplies the (scale_backprop, offset_backprop) buffers."""
+    optionally supplies the (scale_backprop, offset_backprop) buffers.  With
+    `grad_exchange` (a sharding.GradExchange) the parameter gradients come back already
+    summed over all data-parallel ranks."""
     _require(isinstance(y_backprop, torch.Tensor) and y_backprop.dim() > 0,
              "input must be at least 1-dimensional", _shape_str(y_backprop))
     _require(isinstance(x, torch.Tensor) and x.dim() > 0, "input must be at least 1-dimensional",
@@ -236,9 +239,16 @@ def fused_layer_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_spac
     with torch.cuda.device(x.device):
         lib = _lib.load()
         ws_ptr, ws_bytes = _workspace(x.device, lib.nvn_ln_bwd_workspace_bytes(code, N, D))
-        st = lib.nvn_ln_bwd(code, dy.data_ptr(), x.data_ptr(), scale.data_ptr(), mean.data_ptr(),
-                            inv_std.data_ptr(), N, D, dx.data_ptr(), dgamma.data_ptr(),
-                            dbeta.data_ptr(), ws_ptr, ws_bytes, _stream(x.device))
+        if grad_exchange is None:
+            st = lib.nvn_ln_bwd(code, dy.data_ptr(), x.data_ptr(), scale.data_ptr(),
+                                mean.data_ptr(), inv_std.data_ptr(), N, D, dx.data_ptr(),
+                                dgamma.data_ptr(), dbeta.data_ptr(), ws_ptr, ws_bytes,
+                                _stream(x.device))
+        else:
+            st = lib.nvn_ln_bwd_dp(code, dy.data_ptr(), x.data_ptr(), scale.data_ptr(),
+                                   mean.data_ptr(), inv_std.data_ptr(), N, D, dx.data_ptr(),
+                                   dgamma.data_ptr(), dbeta.data_ptr(), ws_ptr, ws_bytes,
+                                   grad_exchange.next_comm(), _stream(x.device))
     _check(st, "nvn_ln_bwd")
     return dx, dgamma, dbeta
 
@@ -277,7 +287,8 @@ def fused_instance_norm_op(x, scale, offset, data_format: str = "N...C", epsilon
 
 
 def fused_instance_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_space_2,
-                                data_format: str = "N...C", epsilon: float = 0.001, out_grads=None):
+                                data_format: str = "N...C", epsilon: float = 0.001, out_grads=None,
+                                grad_exchange=None):
     """FusedInstanceNormGrad (norm_ops.cc:189-202): returns (x_backprop, scale_backprop,
     offset_backprop).  `out_grads` optionally supplies the two parameter-gradient buffers."""
     _require(isinstance(y_backprop, torch.Tensor) and y_backprop.dim() > 3,
@@ -309,9 +320,16 @@ def fused_instance_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_s
     with torch.cuda.device(x.device):
         lib = _lib.load()
         ws_ptr, ws_bytes = _workspace(x.device, lib.nvn_in_bwd_workspace_bytes(code, N, C, D, int(cf)))
-        st = lib.nvn_in_bwd(code, dy.data_ptr(), x.data_ptr(), scale.data_ptr(), mean.data_ptr(),
-                            inv_std.data_ptr(), N, C, D, int(cf), dx.data_ptr(), dgamma.data_ptr(),
-                            dbeta.data_ptr(), ws_ptr, ws_bytes, _stream(x.device))
+        if grad_exchange is None:
+            st = lib.nvn_in_bwd(code, dy.data_ptr(), x.data_ptr(), scale.data_ptr(),
+                                mean.data_ptr(), inv_std.data_ptr(), N, C, D, int(cf),
+                                dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), ws_ptr,
+                                ws_bytes, _stream(x.device))
+        else:
+            st = lib.nvn_in_bwd_dp(code, dy.data_ptr(), x.data_ptr(), scale.data_ptr(),
+                                   mean.data_ptr(), inv_std.data_ptr(), N, C, D, int(cf),
+                                   dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), ws_ptr,
+                                   ws_bytes, grad_exchange.next_comm(), _stream(x.device))
     _check(st, "nvn_in_bwd")
     return dx, dgamma, dbeta
 

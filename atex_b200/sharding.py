@@ -10,10 +10,13 @@ over NVLink on GPUs, gloo in CPU tests).
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Tuple
 
 import torch
 import torch.distributed as dist
+
+from . import _lib
 
 
 def shard_range(total: int, rank: int, world: int) -> Tuple[int, int]:
@@ -47,3 +50,71 @@ def allreduce_param_grads(dgamma: torch.Tensor, dbeta: torch.Tensor, group=None,
     buffer[F:].copy_(dbeta.reshape(-1))
     dist.all_reduce(buffer, op=dist.ReduceOp.SUM, group=group)
     return buffer[:F].view(dgamma.shape), buffer[F:].view(dbeta.shape)
+
+
+class GradExchange:
+    """Peer-memory buffers for the fused column-reduce + all-reduce of [dgamma | dbeta].
+
+    Pass an instance as ``grad_exchange=`` to ``fused_layer_norm_grad_op`` /
+    ``fused_instance_norm_grad_op``: the last kernel of the backward pass then writes this
+    rank's parameter-gradient vector into every rank's receive buffer over NVLink and adds
+    the ``world`` vectors in rank order, so the op returns the global sums and no separate
+    collective runs.  Every rank must make the same sequence of calls (same F).
+
+    The receive buffers come from torch's symmetric memory (one allocation per rank, mapped
+    into every peer).  Without a process group (single GPU) plain device
+    memory is used and the exchange degenerates to a copy through the rank's own buffer.
+    """
+
+    def __init__(self, features: int, device: torch.device, group=None, deferred: bool = False):
+        """deferred=True: the backward op only pushes this rank's vector; call finish()
+        (typically on a side stream, see bench.py) to wait for the peers and obtain the sums.
+        Start the backward op of step e + 1 only after finish() of step e - 2 has completed
+        on this rank (the receive slots are reused every fourth step)."""
+        lib = _lib.load()
+        self.deferred = bool(deferred)
+        self.features = int(features)
+        if self.features % 2:
+            raise ValueError("the fused exchange needs an even number of features")
+        self.device = torch.device(device)
+        distributed = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if distributed else 1
+        self.rank = dist.get_rank(group) if distributed else 0
+        if self.world > _lib.NVN_DP_MAX_RANKS:
+            raise ValueError(f"at most {_lib.NVN_DP_MAX_RANKS} ranks")
+        recv_bytes = lib.nvn_dp_recv_bytes(self.features, self.world)
+        self.epoch = 0
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            grp = group if group is not None else dist.group.WORLD
+            self._recv = symm_mem.empty(recv_bytes // 4, dtype=torch.int32, device=self.device)
+            self._recv.zero_()
+            self._h_recv = symm_mem.rendezvous(self._recv, grp)
+            recv_ptrs = list(self._h_recv.buffer_ptrs)
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group)  # every rank's buffer is zero before anyone pushes
+        else:
+            self._recv = torch.zeros(recv_bytes // 4, dtype=torch.int32, device=self.device)
+            recv_ptrs = [self._recv.data_ptr()]
+        self._comm = _lib.DpComm()
+        self._comm.rank = self.rank
+        self._comm.world = self.world
+        self._comm.defer = 1 if self.deferred else 0
+        for i in range(self.world):
+            self._comm.recv[i] = recv_ptrs[i]
+
+    def next_comm(self):
+        """ctypes pointer to the nvn_dp_comm for the next call (advances the epoch)."""
+        self.epoch += 1
+        self._comm.epoch = self.epoch
+        return ctypes.byref(self._comm)
+
+    def finish(self, dgamma: torch.Tensor, dbeta: torch.Tensor, stream=None) -> None:
+        """Deferred mode: complete the exchange of the most recent backward call into
+        dgamma / dbeta on `stream` (default: the current stream)."""
+        st = stream if stream is not None else torch.cuda.current_stream(self.device)
+        with torch.cuda.device(self.device):
+            rc = _lib.load().nvn_dp_finish(self.features, ctypes.byref(self._comm),
+                                           dgamma.data_ptr(), dbeta.data_ptr(), st.cuda_stream)
+        if rc != _lib.NVN_OK:
+            raise RuntimeError(f"nvn_dp_finish: {_lib.status_string(rc)}")

@@ -53,6 +53,10 @@ def parse_args():
     p.add_argument("--graph", action="store_true",
                    help="replay the timed steps from a CUDA graph (removes host launch overhead; "
                         "meant for the small workloads c1 / c3c)")
+    p.add_argument("--collective", default="fused-async", choices=["fused-async", "fused", "nccl"],
+                   help="N > 1: 'fused' exchanges dgamma|dbeta inside the last backward kernel over "
+                        "peer memory; 'fused-async' pushes there and completes the exchange on a "
+                        "side stream while the next forward runs; 'nccl' is a separate NCCL all-reduce")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     return p.parse_args()
@@ -159,7 +163,12 @@ def workload_config(w, args, world):
         "workload": f"{w.name}: {'LayerNorm' if w.op == 'ln' else 'InstanceNorm ' + w.data_format} "
                     f"{w.dtype} {list(w.shape())} per GPU, eps={w.eps}, fwd+bwd",
         "per_gpu_batch": w.N, "global_batch": w.N * (world if args.scaling == "weak" else 1),
-        "parallelism": f"dp{world}", "collective": "all_reduce(dgamma|dbeta)" if world > 1 else "none",
+        "parallelism": f"dp{world}",
+        "collective": ("none" if world == 1 else
+                       "all-reduce of dgamma|dbeta fused into the column-reduce kernel (peer memory)"
+                       if args.collective == "fused" else
+                       "dgamma|dbeta pushed to peers by the column-reduce kernel, summed on a side stream"
+                       if args.collective == "fused-async" else "NCCL all_reduce(dgamma|dbeta)"),
         "l2": "inputs larger than L2; buffer sets rotated",
     }
 
@@ -277,31 +286,56 @@ def main():
     grad_buf = torch.empty(2 * F, dtype=torch.float32, device=dev)
     grad_views = (grad_buf[:F], grad_buf[F:])
 
+    exchange = None
+    deferred = args.collective == "fused-async"
+    if world > 1 and args.collective != "nccl" and F % 2 == 0:
+        exchange = sharding.GradExchange(F, dev, deferred=deferred)
+    side = torch.cuda.Stream(device=dev) if (exchange is not None and deferred) else None
+    fin_ev = [torch.cuda.Event() for _ in range(4)]
+    push_ev = [torch.cuda.Event() for _ in range(4)]
+    pending = {"n": 0}
     if w.op == "ln":
         def fwd(x):
             return A.fused_layer_norm_op(x, gamma, beta, axis=[-1], epsilon=w.eps)
 
         def bwd(dy, x, m, s):
-            return A.fused_layer_norm_grad_op(dy, x, gamma, m, s, axis=[-1], out_grads=grad_views)
+            return A.fused_layer_norm_grad_op(dy, x, gamma, m, s, axis=[-1], out_grads=grad_views,
+                                              grad_exchange=exchange)
     else:
         def fwd(x):
             return A.fused_instance_norm_op(x, gamma, beta, data_format=w.data_format, epsilon=w.eps)
 
         def bwd(dy, x, m, s):
             return A.fused_instance_norm_grad_op(dy, x, gamma, m, s, data_format=w.data_format,
-                                                 out_grads=grad_views)
+                                                 out_grads=grad_views, grad_exchange=exchange)
 
     def step(i, ev=None):
         x, dy = xs[i % nsets], dys[i % nsets]
         y, m, s = fwd(x)
         if ev is not None:
             ev[0].record()
+        main = torch.cuda.current_stream()
+        if side is not None and pending["n"] > 1:
+            # receive slots are reused every fourth step: staying at most two finishes
+            # ahead keeps every slot's readers done before it is overwritten
+            main.wait_event(fin_ev[(pending["n"] - 2) % 4])
         dx, dg, db = bwd(dy, x, m, s)
         if ev is not None:
             ev[1].record()
-        if world > 1:
+        if side is not None:
+            k = pending["n"] % 4
+            push_ev[k].record(main)
+            side.wait_event(push_ev[k])
+            exchange.finish(grad_views[0], grad_views[1], stream=side)
+            fin_ev[k].record(side)
+            pending["n"] += 1
+        if world > 1 and exchange is None:
             dist.all_reduce(grad_buf)
         return y, dx, dg, db
+
+    def drain():
+        if side is not None and pending["n"] > 0:
+            torch.cuda.current_stream().wait_event(fin_ev[(pending["n"] - 1) % 4])
 
     def barrier():
         torch.cuda.synchronize()
@@ -351,6 +385,7 @@ def main():
     for i in range(K):
         starts[i].record()
         step(i, mids[i])
+    drain()
     e1.record()
     barrier()
     t_wall1 = time.perf_counter()
@@ -378,7 +413,15 @@ def main():
             dyd.copy_(dy_h, non_blocking=True)
             y, m, s = fwd(xd)
             dx, dg, db = bwd(dyd, xd, m, s)
-            if world > 1:
+            if side is not None:
+                k = pending["n"] % 4
+                push_ev[k].record(torch.cuda.current_stream())
+                side.wait_event(push_ev[k])
+                exchange.finish(grad_views[0], grad_views[1], stream=side)
+                fin_ev[k].record(side)
+                pending["n"] += 1
+                drain()
+            if world > 1 and exchange is None:
                 dist.all_reduce(grad_buf)
             out_h.copy_(grad_buf, non_blocking=True)
 

@@ -166,6 +166,55 @@ NVN_API int nvn_in_bwd(int dtype, const void* dy, const void* x, const float* ga
                        float* dbeta, void* workspace, size_t workspace_bytes,
                        void* stream);
 
+/* ---- data-parallel backward: column reduction fused with the all-reduce -------
+ * One process per GPU, every rank calling with the same N-shard shapes.  Instead of
+ * finishing with a local dgamma / dbeta that the caller must all-reduce, the last
+ * kernel of the backward pass exchanges the per-rank vectors over NVLink peer memory
+ * and every rank ends up with the global sums (bit-identical on all ranks).
+ *
+ * The caller provides, for every rank r, a receive buffer that all ranks can address
+ * (peer-mapped / symmetric memory, e.g. from cudaIpc*, cuMem* or torch's symmetric memory):
+ *   recv[r] : nvn_dp_recv_bytes(F, world) bytes, 16-byte aligned, zero-filled once before
+ *             the first call
+ * in rank order (recv[rank] is this rank's own).  `epoch` must be 1 on the first call and
+ * grow by one per call, the same on all ranks; calls of one communicator must not overlap
+ * on a GPU.  F must be even.  Device-side waits are bounded: if a peer never shows up the
+ * kernel gives up, nvn_device_status() reports NVN_ERR_TIMEOUT and the gradients of that
+ * call are undefined.  world == 1 is allowed (pure self-exchange).
+ * No counterpart in the reference (its ops are single-device, norm_ops.cc has no
+ * collective); this replaces the separate all-reduce of a data-parallel job. */
+#define NVN_DP_MAX_RANKS 16
+typedef struct nvn_dp_comm {
+  int rank;
+  int world;
+  void* recv[NVN_DP_MAX_RANKS];
+  uint32_t epoch;
+  int defer; /* 0: the backward call completes the exchange.  1: it only reduces and pushes;
+                nvn_dp_finish (same comm contents) waits and writes dgamma / dbeta later. */
+} nvn_dp_comm;
+
+/* Second half of a deferred exchange (comm->defer was 1 in the backward call of this
+ * epoch): waits - bounded - for every rank's push of `comm->epoch` and writes the summed
+ * dgamma / dbeta (F floats each).  May run on another stream than the backward call, after
+ * it in stream / event order.  The caller must not start the backward call of epoch e + 1
+ * on a rank before that rank's nvn_dp_finish of epoch e - 2 has completed (a receive slot
+ * is reused every fourth epoch). */
+NVN_API int nvn_dp_finish(int64_t F, const nvn_dp_comm* comm, float* dgamma, float* dbeta,
+                          void* stream);
+
+NVN_API size_t nvn_dp_recv_bytes(int64_t F, int world);
+
+NVN_API int nvn_ln_bwd_dp(int dtype, const void* dy, const void* x, const float* gamma,
+                          const float* mean, const float* inv_std, int64_t N, int64_t D,
+                          void* dx, float* dgamma, float* dbeta, void* workspace,
+                          size_t workspace_bytes, const nvn_dp_comm* comm, void* stream);
+
+NVN_API int nvn_in_bwd_dp(int dtype, const void* dy, const void* x, const float* gamma,
+                          const float* mean, const float* inv_std, int64_t N, int64_t C,
+                          int64_t D, int channel_first, void* dx, float* dgamma, float* dbeta,
+                          void* workspace, size_t workspace_bytes, const nvn_dp_comm* comm,
+                          void* stream);
+
 /* ---- LayerNorm backward without a caller-provided workspace ------------------
  * Same computation and results as nvn_ln_bwd, for callers that cannot supply
  * scratch memory: a plugin callback that receives only input and output
