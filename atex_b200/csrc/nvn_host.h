@@ -51,8 +51,8 @@ int* device_status_word();
 
 // Row-group shapes: X(index, TPR, VPT, CS, RB, PR, MINB, PF)
 //   TPR threads per row, VPT vectors per thread, CS CTAs per cluster, RB rows in
-//   flight per row group, PR gamma/beta cached in registers, MINB minimum CTAs per
-//   SM requested from the compiler (0 = no request), PF load mode: 0 = plain loads,
+//   flight per row group, PR gamma/beta cached in registers, MINB the CTA size for
+//   row groups smaller than a CTA (0 = 256 threads), PF load mode: 0 = plain loads,
 //   1 = register prefetch of the next row batch, >= 2 = TMA (cp.async.bulk) ring in
 //   shared memory with that many stages.
 // "Light" kernels keep only the row itself in registers (LayerNorm forward,
@@ -71,9 +71,9 @@ int* device_status_word();
 
 #ifndef NVN_ROW_SHAPES_HEAVY
 #define NVN_ROW_SHAPES_HEAVY(X)                                                              \
-  X(0, 4, 1, 1, 2, 1, 0, 1)     X(1, 8, 1, 1, 2, 1, 0, 1)     X(2, 16, 1, 1, 2, 1, 0, 1)     \
-  X(3, 32, 1, 1, 2, 1, 0, 1)    X(4, 32, 2, 1, 2, 1, 0, 1)    X(5, 128, 1, 1, 2, 1, 0, 1)    \
-  X(6, 128, 2, 1, 2, 0, 0, 1)   X(7, 256, 2, 1, 2, 1, 0, 1)   X(8, 512, 2, 1, 1, 1, 0, 1)    \
+  X(0, 4, 1, 1, 4, 1, 128, 3)   X(1, 8, 1, 1, 4, 1, 128, 3)   X(2, 16, 1, 1, 4, 1, 128, 3)   \
+  X(3, 32, 1, 1, 4, 1, 128, 3)  X(4, 32, 2, 1, 2, 1, 128, 3)  X(5, 64, 2, 1, 2, 1, 128, 3)   \
+  X(6, 64, 4, 1, 1, 1, 128, 1)  X(7, 256, 2, 1, 2, 1, 0, 1)   X(8, 512, 2, 1, 1, 1, 0, 1)    \
   X(9, 512, 2, 2, 1, 1, 0, 1)   X(10, 512, 2, 4, 1, 1, 0, 1)  X(11, 256, 4, 8, 1, 1, 0, 1)   \
   X(12, 512, 2, 16, 1, 1, 0, 1) X(13, 512, 4, 16, 1, 0, 0, 1)
 #endif

@@ -31,9 +31,12 @@
 
 namespace nvn {
 
-template <int TPR>
+// Threads per CTA: a row group when it is at least BLK threads, otherwise as many row
+// groups as fill BLK threads (BLK == 0 selects the default of 256).
+template <int TPR, int BLK>
 struct RowBlock {
-  static constexpr int kBlock = TPR >= 256 ? TPR : 256;
+  static constexpr int kMin = BLK == 0 ? 256 : BLK;
+  static constexpr int kBlock = TPR >= kMin ? TPR : kMin;
   static constexpr int kRowsPerCta = kBlock / TPR;
 };
 
@@ -46,7 +49,8 @@ struct RowBlock {
 //         their reductions share one barrier
 //   PR    keep gamma (and beta) for the thread's columns in registers for the whole
 //         kernel instead of re-reading them (L1 / L2 hits) for every row
-//   MINB  minimum resident CTAs per SM asked of the compiler (register cap)
+//   MINB  CTA size when a row group is smaller than that: 0 = 256 threads, else the value
+//         (128 gives finer-grained CTAs: fewer row groups share a barrier)
 //   PF    load mode.  0: plain loads at the top of each iteration.  1: register prefetch -
 //         the loads of the next row batch are issued as soon as the current batch has been
 //         converted to fp32, so they are in flight during the reductions and the stores.
@@ -216,10 +220,10 @@ __device__ __forceinline__ void ring_give_up(Ring& ring, int* status, int64_t j,
 // ---------------------------------------------------------------------------
 template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, int PF,
           bool EXACT, bool ROW_AFFINE>
-__global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
+__global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
     rows_fwd_kernel(const RowsArgs a) {
-  constexpr int BLOCK = RowBlock<TPR>::kBlock;
-  constexpr int RPC = RowBlock<TPR>::kRowsPerCta;
+  constexpr int BLOCK = RowBlock<TPR, MINB>::kBlock;
+  constexpr int RPC = RowBlock<TPR, MINB>::kRowsPerCta;
   constexpr bool TMA = PF >= 2;
   constexpr int STAGES = TMA ? PF : 1;
   using Map = VecMap<TPR, VPT, CS, TMA>;
@@ -399,10 +403,10 @@ __global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
 // ---------------------------------------------------------------------------
 template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, int PF,
           bool EXACT, bool ROW_AFFINE>
-__global__ void __launch_bounds__(RowBlock<TPR>::kBlock, MINB)
+__global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
     rows_bwd_kernel(const RowsArgs a) {
-  constexpr int BLOCK = RowBlock<TPR>::kBlock;
-  constexpr int RPC = RowBlock<TPR>::kRowsPerCta;
+  constexpr int BLOCK = RowBlock<TPR, MINB>::kBlock;
+  constexpr int RPC = RowBlock<TPR, MINB>::kRowsPerCta;
   constexpr bool TMA = PF >= 2;
   constexpr int STAGES = TMA ? PF : 1;
   using Map = VecMap<TPR, VPT, CS, TMA>;
@@ -705,8 +709,8 @@ template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MI
           bool EXACT, bool ROW_AFFINE, bool BWD>
 inline cudaError_t launch_rows_exact(const RowsArgs& a, cudaStream_t stream, bool dry_run,
                                      RowsPlan* plan) {
-  constexpr int BLOCK = RowBlock<TPR>::kBlock;
-  constexpr int RPC = RowBlock<TPR>::kRowsPerCta;
+  constexpr int BLOCK = RowBlock<TPR, MINB>::kBlock;
+  constexpr int RPC = RowBlock<TPR, MINB>::kRowsPerCta;
   constexpr bool TMA = PF >= 2;
   size_t ring = 0;
   if constexpr (TMA) {
