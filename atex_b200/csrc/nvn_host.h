@@ -78,17 +78,18 @@ int* device_status_word();
   X(12, 512, 2, 16, 1, 1, 0, 1) X(13, 512, 4, 16, 1, 0, 0, 1)
 #endif
 
-// Scalar (EPV == 1) rows only get a coarse subset: they exist for odd D and
-// misaligned buffers, where correctness matters more than the last GB/s.
+// Rows accessed with less than 128 bits per access (64-, 32-bit or single elements: widths
+// that are not a multiple of the vector, misaligned buffers) share this coarser table.
 #define NVN_ROW_SHAPES_SCALAR(X)                                                             \
-  X(0, 8, 4, 1, 1, 0, 0, 0) X(1, 32, 8, 1, 1, 0, 0, 0) X(2, 256, 8, 1, 1, 0, 0, 0)                    \
-  X(3, 512, 8, 2, 1, 0, 0, 0) X(4, 512, 8, 8, 1, 0, 0, 0) X(5, 512, 8, 16, 1, 0, 0, 0)
+  X(0, 8, 4, 1, 2, 0, 0, 1) X(1, 32, 8, 1, 2, 0, 0, 1) X(2, 256, 8, 1, 1, 0, 0, 1)           \
+  X(3, 512, 8, 2, 1, 0, 0, 1) X(4, 512, 8, 8, 1, 0, 0, 1) X(5, 512, 8, 16, 1, 0, 0, 1)
 
-// One entry point per (dtype, direction) translation unit.  `scalar` selects
-// the EPV == 1 family, `row_affine` the InstanceNorm "NC..." parameter indexing.
+// One entry point per (dtype, direction) translation unit.  `epv` (elements per access: the
+// full 128-bit width, or 4 / 2 / 1) selects the family, `row_affine` the InstanceNorm
+// "NC..." parameter indexing.
 // With dry_run the plan is filled in and nothing is launched.
 #define NVN_DECLARE_ROWS(NAME)                                                              \
-  cudaError_t NAME(bool row_affine, bool scalar, int shape, const RowsArgs& a, cudaStream_t s, \
+  cudaError_t NAME(bool row_affine, int epv, int shape, const RowsArgs& a, cudaStream_t s, \
                    bool dry_run, RowsPlan* plan);
 NVN_DECLARE_ROWS(rows_f32_fwd)
 NVN_DECLARE_ROWS(rows_f32_bwd)

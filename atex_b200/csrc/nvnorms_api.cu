@@ -68,7 +68,28 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 inline size_t dtype_size(int dtype) { return dtype == NVN_F32 ? 4 : 2; }
 inline int full_epv(int dtype) { return dtype == NVN_F32 ? 4 : 8; }
 
-typedef cudaError_t (*RowsFn)(bool, bool, int, const RowsArgs&, cudaStream_t, bool, RowsPlan*);
+typedef cudaError_t (*RowsFn)(bool, int, int, const RowsArgs&, cudaStream_t, bool, RowsPlan*);
+
+// Largest power-of-two alignment (capped at 16) shared by all the pointers given.
+inline size_t common_alignment(std::initializer_list<const void*> ptrs) {
+  uintptr_t bits = 0;
+  for (const void* p : ptrs) bits |= reinterpret_cast<uintptr_t>(p);
+  size_t a = 16;
+  while (a > 1 && (bits & (a - 1)) != 0) a >>= 1;
+  return a;
+}
+
+// Elements per access for rows of width D: the widest of (full, full/2, full/4) that
+// divides D and fits the alignment, else single elements.
+// `align` is the activations' alignment, `par_align` that of the fp32 parameters, which are
+// read e floats at a time in accesses of at most 16 bytes.
+inline int pick_epv(int dtype, int64_t D, size_t align, size_t par_align) {
+  const int V = full_epv(dtype);
+  const size_t es = dtype_size(dtype);
+  for (int e = V; e >= 2; e >>= 1)
+    if (D % e == 0 && e * es <= align && std::min<size_t>(16, e * 4) <= par_align) return e;
+  return 1;
+}
 RowsFn rows_fn(int dtype, bool bwd) {
   switch (dtype) {
     case NVN_F32:
@@ -91,7 +112,8 @@ int fail_cuda(cudaError_t e) {
 // ---------------------------------------------------------------------------
 struct RowProblemPlan {
   bool two_phase;
-  bool scalar;
+  bool scalar;     // two-phase variant runs element-wise
+  int epv;         // elements per access of the row-cached variant
   int shape;       // row-cached variant
   RowsPlan rows;   // filled by a dry run
   R2Plan r2;       // two-phase variant
@@ -100,18 +122,19 @@ struct RowProblemPlan {
   int64_t colpart_rows;  // P of the column reduction (LayerNorm backward / IN backward)
 };
 
-// vec_ok: every pointer is 16-byte aligned (assumed true for size queries).
+// align: alignment shared by every pointer (16 is assumed for size queries).
 int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int64_t N,
-              int64_t C, bool vec_ok, RowProblemPlan* p) {
+              int64_t C, size_t align, size_t par_align, RowProblemPlan* p) {
   memset(p, 0, sizeof(*p));
   const int V = full_epv(dtype);
-  p->scalar = !(vec_ok && D % V == 0);
-  const int epv = p->scalar ? 1 : V;
+  int epv = pick_epv(dtype, D, align, par_align);
+  p->epv = epv;
+  const bool full = epv == V;
   const int64_t nvec = D / epv;
   const bool heavy = bwd && !row_affine;
-  const Shape* table = p->scalar ? kScalarShapes : (heavy ? kHeavyShapes : kLightShapes);
-  const int ntab = p->scalar ? kNumScalar : (heavy ? kNumHeavy : kNumLight);
-  const char* env = p->scalar ? nullptr : (bwd ? "NVN_FORCE_BWD_SHAPE" : "NVN_FORCE_FWD_SHAPE");
+  const Shape* table = !full ? kScalarShapes : (heavy ? kHeavyShapes : kLightShapes);
+  const int ntab = !full ? kNumScalar : (heavy ? kNumHeavy : kNumLight);
+  const char* env = !full ? nullptr : (bwd ? "NVN_FORCE_BWD_SHAPE" : "NVN_FORCE_FWD_SHAPE");
   p->shape = pick_shape(table, ntab, nvec, env);
   p->two_phase = p->shape < 0;
   // Rows that need a cluster could also take the two-phase path (phase 2 then re-reads
@@ -128,7 +151,7 @@ int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int
     a.N = rows;
     a.D = D;
     a.C = C;
-    cudaError_t e = rows_fn(dtype, bwd)(row_affine, p->scalar, p->shape, a, nullptr, true,
+    cudaError_t e = rows_fn(dtype, bwd)(row_affine, p->epv, p->shape, a, nullptr, true,
                                         &p->rows);
     if (e != cudaSuccess) return fail_cuda(e);
     if (bwd) {
@@ -138,6 +161,8 @@ int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int
     }
   } else {
     if (rows > 0x7fffffffLL) return NVN_ERR_UNSUPPORTED;
+    p->scalar = !full;
+    epv = full ? V : 1;
     p->r2 = r2_plan(rows, D, epv, bwd && !row_affine);
     p->off_part = off;
     off += align_up(static_cast<size_t>(rows) * p->r2.nchunks * (bwd ? 2 : 3) * 4, 256);
@@ -156,11 +181,13 @@ int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int
 size_t rows_workspace_bytes(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D,
                             int64_t N, int64_t C) {
   if (rows <= 0 || D <= 0) return 0;
-  RowProblemPlan pv, ps;
+  RowProblemPlan pv;
   size_t b = 0;
-  if (plan_rows(dtype, bwd, row_affine, rows, D, N, C, true, &pv) == NVN_OK) b = pv.bytes;
-  if (plan_rows(dtype, bwd, row_affine, rows, D, N, C, false, &ps) == NVN_OK)
-    b = std::max(b, ps.bytes);
+  // the workspace can depend on the access width, which depends on the caller's alignment
+  for (size_t al : {size_t(16), size_t(8), size_t(4), size_t(2)}) {
+    if (plan_rows(dtype, bwd, row_affine, rows, D, N, C, al, 16, &pv) == NVN_OK)
+      b = std::max(b, pv.bytes);
+  }
   return b;
 }
 
@@ -169,14 +196,10 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
              int64_t rows, int64_t D, int64_t N, int64_t C, float eps, void* out, float* mean,
              float* ivar, float* dgamma, float* dbeta, void* ws, size_t ws_bytes,
              cudaStream_t stream, const nvn_dp_comm* comm = nullptr) {
-  bool vec_ok = aligned(x, 16) && aligned(out, 16) && aligned(gamma, 16);
-  if (bwd) {
-    vec_ok = vec_ok && aligned(dy, 16);
-  } else {
-    vec_ok = vec_ok && aligned(beta, 16);
-  }
+  const size_t align = bwd ? common_alignment({x, out, dy}) : common_alignment({x, out});
+  const size_t par_align = bwd ? common_alignment({gamma}) : common_alignment({gamma, beta});
   RowProblemPlan p;
-  int st = plan_rows(dtype, bwd, row_affine, rows, D, N, C, vec_ok, &p);
+  int st = plan_rows(dtype, bwd, row_affine, rows, D, N, C, align, par_align, &p);
   if (st != NVN_OK) return st;
   if (p.bytes > 0 && (ws == nullptr || !aligned(ws, 256) || ws_bytes < p.bytes))
     return NVN_ERR_WORKSPACE;
@@ -202,7 +225,7 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
     a.status = device_status_word();
     RowsPlan rp;
     cudaError_t e =
-        rows_fn(dtype, bwd)(row_affine, p.scalar, p.shape, a, stream, false, &rp);
+        rows_fn(dtype, bwd)(row_affine, p.epv, p.shape, a, stream, false, &rp);
     if (e != cudaSuccess) return fail_cuda(e);
   } else {
     R2Args a = {};
@@ -639,7 +662,7 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
   }
   const int64_t rows = is_in ? N * C : N;
   RowProblemPlan p;
-  int st = plan_rows(dtype, bwd, is_in, rows, D, N, is_in ? C : 1, true, &p);
+  int st = plan_rows(dtype, bwd, is_in, rows, D, N, is_in ? C : 1, 16, 16, &p);
   if (st != NVN_OK) return st;
   if (p.two_phase) {
     snprintf(out, out_bytes, "rows two-phase epv=%d chunk=%lld nchunks=%d slices=%d",

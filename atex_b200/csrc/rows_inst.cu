@@ -25,16 +25,29 @@ using T = __nv_bfloat16;
 
 namespace nvn {
 
-cudaError_t NVN_CAT3(rows, NVN_TNAME, NVN_DIR)(bool row_affine, bool scalar, int shape,
+template <int EPV>
+static cudaError_t coarse(bool row_affine, int shape, const RowsArgs& a, cudaStream_t s,
+                          bool dry_run, RowsPlan* plan) {
+  constexpr bool BWD = NVN_BWD != 0;
+  return row_affine ? launch_rows_coarse<T, EPV, true, BWD>(shape, a, s, dry_run, plan)
+                    : launch_rows_coarse<T, EPV, false, BWD>(shape, a, s, dry_run, plan);
+}
+
+cudaError_t NVN_CAT3(rows, NVN_TNAME, NVN_DIR)(bool row_affine, int epv, int shape,
                                                 const RowsArgs& a, cudaStream_t s, bool dry_run,
                                                 RowsPlan* plan) {
   constexpr bool BWD = NVN_BWD != 0;
-  if (scalar) {
-    return row_affine ? launch_rows_scalar<T, true, BWD>(shape, a, s, dry_run, plan)
-                      : launch_rows_scalar<T, false, BWD>(shape, a, s, dry_run, plan);
+  constexpr int V = VecTraits<T>::kFull;
+  if (epv == V) {
+    return row_affine ? launch_rows_vec<T, true, BWD>(shape, a, s, dry_run, plan)
+                      : launch_rows_vec<T, false, BWD>(shape, a, s, dry_run, plan);
   }
-  return row_affine ? launch_rows_vec<T, true, BWD>(shape, a, s, dry_run, plan)
-                    : launch_rows_vec<T, false, BWD>(shape, a, s, dry_run, plan);
+  if (epv == 1) return coarse<1>(row_affine, shape, a, s, dry_run, plan);
+  if (epv == 2) return coarse<2>(row_affine, shape, a, s, dry_run, plan);
+  if constexpr (V == 8) {
+    if (epv == 4) return coarse<4>(row_affine, shape, a, s, dry_run, plan);
+  }
+  return cudaErrorInvalidValue;
 }
 
 }  // namespace nvn

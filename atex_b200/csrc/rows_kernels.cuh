@@ -718,7 +718,7 @@ inline cudaError_t launch_rows_exact(const RowsArgs& a, cudaStream_t stream, boo
     ring = row_bytes * (CS == 1 ? RPC * RB : RB) * (BWD ? 2 : 1) * PF;
     // rows that would need too large a ring, or clusters on rows that do not fill the
     // shape, fall back to the register-prefetch twin of this shape
-    if (ring > kMaxRingBytes || (CS > 1 && !EXACT))
+    if (ring > kMaxRingBytes || (CS > 1 && !EXACT) || sizeof(Pack<T, EPV>) < 16)
       return launch_rows_exact<T, EPV, TPR, VPT, CS, RB, PR, MINB, 1, EXACT, ROW_AFFINE, BWD>(
           a, stream, dry_run, plan);
   }
@@ -829,13 +829,15 @@ cudaError_t launch_rows_vec(int shape, const RowsArgs& a, cudaStream_t s, bool d
 #undef X
 }
 
-template <typename T, bool ROW_AFFINE, bool BWD>
-cudaError_t launch_rows_scalar(int shape, const RowsArgs& a, cudaStream_t s, bool dry,
+// Narrower accesses (EPV below a full 128-bit vector, down to single elements) exist for
+// rows whose width or alignment rules out 128-bit accesses.  They share one coarse table.
+template <typename T, int EPV, bool ROW_AFFINE, bool BWD>
+cudaError_t launch_rows_coarse(int shape, const RowsArgs& a, cudaStream_t s, bool dry,
                                RowsPlan* p) {
   switch (shape) {
 #define X(I, TPR, VPT, CS, RB, PR, MINB, PF) \
   case I:                                    \
-    return launch_rows_one<T, 1, TPR, VPT, CS, RB, PR != 0, MINB, PF, ROW_AFFINE, BWD>( \
+    return launch_rows_one<T, EPV, TPR, VPT, CS, RB, PR != 0, MINB, PF, ROW_AFFINE, BWD>( \
         a, s, dry, p);
     NVN_ROW_SHAPES_SCALAR(X)
 #undef X

@@ -35,6 +35,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# DRAM traffic of one backward launch (dram__bytes_read + dram__bytes_write) taken from the
+# ncu capture summarised in profiles/rows_c2_ncu_full.md: 368.3 MB for 16384 rows of c2,
+# i.e. 22 478 bytes per row (traffic grows in proportion to the rows).  Only known for c2.
+NCU_BWD_TRAFFIC_BYTES_PER_ROW = {"c2": 368.3e6 / 16384}
+
 NOMINAL_PEAK_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
 
@@ -462,7 +467,9 @@ def main():
     code = {"f32": 0, "f16": 1, "bf16": 2}[w.dtype]
     roofline = {
         "bound": "hbm", "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak,
-        "peak_kind": peak_kind, "traffic": None,
+        "peak_kind": peak_kind,
+        "traffic": (NCU_BWD_TRAFFIC_BYTES_PER_ROW[w.name] * wl.N
+                    if w.name in NCU_BWD_TRAFFIC_BYTES_PER_ROW else None),
         "kernel": f"{w.op}_bwd: " + _lib.describe_plan(opn + 1, code, wl.N, w.C, w.D, int(w.channel_first)),
         "algorithmic_bytes_per_launch": bwd_bytes, "ms_per_launch": bwd_ms,
         "forward": {"achieved": fwd_gbs, "frac": fwd_gbs / peak, "ms_per_launch": fwd_ms,

@@ -256,6 +256,47 @@ def test_misaligned_buffers_take_the_scalar_path_and_stay_correct(dtype):
     assert T.grad_param_error(dg2, T.to_float64(dg1))[0] <= 1.0
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,D", [(300, 100), (1000, 12), (64, 1028), (9, 36868), (257, 50), (33, 1026),
+                                 (5, 6), (3, 70002)])
+def test_widths_that_only_allow_narrower_accesses(dtype, N, D):
+    """Widths that are a multiple of half or a quarter of the 128-bit vector, but not of the
+    vector itself, run with 64- / 32-bit accesses instead of element by element."""
+    code = {"f32": _lib.NVN_F32, "f16": _lib.NVN_F16, "bf16": _lib.NVN_BF16}[dtype]
+    full = 4 if dtype == "f32" else 8
+    want = next((e for e in (full, full // 2, full // 4) if e >= 2 and D % e == 0), 1)
+    for op in (0, 1):
+        plan = _lib.describe_plan(op, code, N, 1, D, 0)
+        assert f"epv={want} " in plan, plan
+    x, dy, g, b = rand_ln(N, D, dtype, seed=N + D)
+    check_ln(x, dy, g, b, 1e-3)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_half_aligned_buffers_use_half_width_accesses_and_stay_in_bounds(dtype):
+    """Buffers aligned to 8 bytes only: canaries catch a 16-byte store that ignores it."""
+    dt = T.TORCH_DTYPE[dtype]
+    N, D = 53, 512
+    shift = 8 // torch.empty((), dtype=dt).element_size()
+    x, dy, g, b = rand_ln(N, D, dtype, seed=5)
+    big = torch.full((N * D + 2 * shift,), 7.0, device=DEV, dtype=dt)
+    xv = big[shift:shift + N * D].view(N, D)
+    xv.copy_(x.to(DEV))
+    assert xv.data_ptr() % 16 == 8
+    outbuf = torch.full((N * D + 2 * shift,), -3.0, device=DEV, dtype=dt)
+    yv = outbuf[shift:shift + N * D].view(N, D)
+    y, m, s = A.fused_layer_norm_op(xv, g.to(DEV), b.to(DEV), out=yv)
+    y_ref, m_ref, s_ref = A.fused_layer_norm_op(x.to(DEV), g.to(DEV), b.to(DEV))
+    dx, dg, db = A.fused_layer_norm_grad_op(dy.to(DEV), xv, g.to(DEV), m_ref, s_ref)
+    dx1, dg1, db1 = A.fused_layer_norm_grad_op(dy.to(DEV), x.to(DEV), g.to(DEV), m_ref, s_ref)
+    torch.cuda.synchronize()
+    assert (outbuf[:shift] == -3.0).all().item() and (outbuf[-shift:] == -3.0).all().item()
+    assert T.activation_error(y, T.to_float64(y_ref), dtype)[0] <= 1.0
+    assert T.activation_error(dx, T.to_float64(dx1), dtype)[0] <= 1.0
+    assert T.grad_param_error(dg, T.to_float64(dg1))[0] <= 1.0
+    assert T.grad_param_error(db, T.to_float64(db1))[0] <= 1.0
+
+
 def test_backward_uses_the_statistics_it_is_given():
     """The gradient op must consume the passed-in mean / inverse std, not recompute them
     (the reference's tests feed statistics computed elsewhere, fused_layer_norm_test.py:97-108)."""
