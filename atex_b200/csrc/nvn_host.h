@@ -40,7 +40,8 @@ struct RowsPlan {
   int vpt;
   int epv;
   int rb;
-  int load_mode;  // 0 plain, 1 register prefetch, >= 2 TMA ring with that many stages
+  int load_mode;  // 0 plain, 1 register prefetch, 2..9 TMA ring with that many stages,
+                  // >= 10 held TMA ring with (load_mode - 10) stages
   int partial_rows;  // rows of [2][D] dgamma/dbeta partials the backward kernel writes
 };
 
@@ -53,8 +54,9 @@ int* device_status_word();
 //   TPR threads per row, VPT vectors per thread, CS CTAs per cluster, RB rows in
 //   flight per row group, PR gamma/beta cached in registers, MINB the CTA size for
 //   row groups smaller than a CTA (0 = 256 threads), PF load mode: 0 = plain loads,
-//   1 = register prefetch of the next row batch, >= 2 = TMA (cp.async.bulk) ring in
-//   shared memory with that many stages.
+//   1 = register prefetch of the next row batch, 2..9 = TMA (cp.async.bulk) ring in
+//   shared memory with that many stages, 10 + s = (backward) held ring of s stages: the
+//   row batch stays in its stage until dx is written and is read from there twice.
 // "Light" kernels keep only the row itself in registers (LayerNorm forward,
 // InstanceNorm forward/backward); "heavy" is LayerNorm backward, which adds the
 // per-column dgamma/dbeta accumulators and therefore spreads a row over more
@@ -69,13 +71,20 @@ int* device_status_word();
   X(12, 512, 8, 4, 1, 0, 0, 1)  X(13, 512, 8, 8, 1, 0, 0, 1)  X(14, 512, 8, 16, 1, 0, 0, 1)
 #endif
 
+// In the heavy table a held-ring entry (PF >= 10) is followed by the register-prefetch
+// entry of the same capacity: the held ring wins once the problem is large enough to be
+// bandwidth-bound, the other on small problems, where the ring's start-up shows.
 #ifndef NVN_ROW_SHAPES_HEAVY
 #define NVN_ROW_SHAPES_HEAVY(X)                                                              \
-  X(0, 4, 1, 1, 4, 1, 128, 3)   X(1, 8, 1, 1, 4, 1, 128, 3)   X(2, 16, 1, 1, 4, 1, 128, 3)   \
-  X(3, 32, 1, 1, 4, 1, 128, 3)  X(4, 32, 2, 1, 2, 1, 128, 3)  X(5, 64, 2, 1, 2, 1, 128, 3)   \
-  X(6, 64, 4, 1, 1, 1, 128, 1)  X(7, 256, 2, 1, 2, 1, 0, 1)   X(8, 512, 2, 1, 1, 1, 0, 1)    \
-  X(9, 512, 2, 2, 1, 1, 0, 1)   X(10, 512, 2, 4, 1, 1, 0, 1)  X(11, 256, 4, 8, 1, 1, 0, 1)   \
-  X(12, 512, 2, 16, 1, 1, 0, 1) X(13, 512, 4, 16, 1, 0, 0, 1)
+  X(0, 4, 1, 1, 4, 1, 128, 3)      X(1, 8, 1, 1, 4, 1, 128, 3)     X(2, 16, 1, 1, 4, 1, 128, 3) \
+  X(3, 32, 1, 1, 4, 1, 128, 3)     X(4, 32, 2, 1, 2, 1, 128, 3)    X(5, 64, 2, 1, 2, 1, 128, 3) \
+  X(6, 128, 2, 1, 2, 1, 128, 12)   X(7, 64, 4, 1, 1, 1, 128, 1)                                \
+  X(8, 128, 4, 1, 1, 1, 128, 13)   X(9, 256, 2, 1, 2, 1, 0, 1)                                 \
+  X(10, 256, 4, 1, 1, 1, 0, 12)    X(11, 512, 2, 1, 1, 1, 0, 1)                                \
+  X(12, 512, 4, 1, 1, 0, 0, 12)    X(13, 512, 2, 2, 1, 1, 0, 1)                                \
+  X(14, 128, 4, 8, 2, 1, 128, 12)  X(15, 512, 2, 4, 1, 1, 0, 1)                                \
+  X(16, 128, 4, 16, 2, 1, 128, 12) X(17, 256, 4, 8, 1, 1, 0, 1)                                \
+  X(18, 512, 2, 16, 1, 1, 0, 1)    X(19, 512, 4, 16, 1, 0, 0, 1)
 #endif
 
 // Rows accessed with less than 128 bits per access (64-, 32-bit or single elements: widths

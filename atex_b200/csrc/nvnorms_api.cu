@@ -29,9 +29,9 @@ thread_local int t_last_cuda_error = 0;
 std::atomic<int> g_sm_count{0};
 
 struct Shape {
-  int tpr, vpt, cs;
+  int tpr, vpt, cs, pf;
 };
-#define X(I, TPR, VPT, CS, RB, PR, MINB, PF) {TPR, VPT, CS},
+#define X(I, TPR, VPT, CS, RB, PR, MINB, PF) {TPR, VPT, CS, PF},
 const Shape kLightShapes[] = {NVN_ROW_SHAPES_LIGHT(X)};
 const Shape kHeavyShapes[] = {NVN_ROW_SHAPES_HEAVY(X)};
 const Shape kScalarShapes[] = {NVN_ROW_SHAPES_SCALAR(X)};
@@ -42,10 +42,17 @@ constexpr int kNumScalar = sizeof(kScalarShapes) / sizeof(Shape);
 
 inline int64_t cap(const Shape& s) { return static_cast<int64_t>(s.tpr) * s.vpt * s.cs; }
 
-// Smallest capacity that holds `nvec` vectors; among equals the first listed.
+// Bytes per tensor from which a held-ring shape is preferred over its register-prefetch
+// twin (between [4096, 1024] fp32, 17 MB, where the twin is 25 % faster, and
+// [65536, 2048] bf16, 268 MB, where the held ring is 15 % faster).
+constexpr int64_t kHeldRingMinBytes = 64ll << 20;
+
+// Smallest capacity that holds `nvec` vectors; among equals the first listed, skipping
+// held-ring entries for problems of less than kHeldRingMinBytes per tensor.
 // NVN_FORCE_FWD_SHAPE / NVN_FORCE_BWD_SHAPE (a table index) override the
 // choice when that shape is large enough: used for tuning runs only.
-int pick_shape(const Shape* table, int n, int64_t nvec, const char* force_env) {
+int pick_shape(const Shape* table, int n, int64_t nvec, int64_t tensor_bytes,
+               const char* force_env) {
   if (force_env != nullptr) {
     const char* v = getenv(force_env);
     if (v != nullptr && *v != '\0') {
@@ -54,9 +61,13 @@ int pick_shape(const Shape* table, int n, int64_t nvec, const char* force_env) {
     }
   }
   int best = -1;
-  for (int i = 0; i < n; ++i) {
-    if (cap(table[i]) < nvec) continue;
-    if (best < 0 || cap(table[i]) < cap(table[best])) best = i;
+  for (int pass = 0; pass < 2 && best < 0; ++pass) {
+    for (int i = 0; i < n; ++i) {
+      if (cap(table[i]) < nvec) continue;
+      // first pass: leave held rings out for small problems; second pass: anything
+      if (pass == 0 && table[i].pf >= 10 && tensor_bytes < kHeldRingMinBytes) continue;
+      if (best < 0 || cap(table[i]) < cap(table[best])) best = i;
+    }
   }
   return best;
 }
@@ -135,7 +146,7 @@ int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int
   const Shape* table = !full ? kScalarShapes : (heavy ? kHeavyShapes : kLightShapes);
   const int ntab = !full ? kNumScalar : (heavy ? kNumHeavy : kNumLight);
   const char* env = !full ? nullptr : (bwd ? "NVN_FORCE_BWD_SHAPE" : "NVN_FORCE_FWD_SHAPE");
-  p->shape = pick_shape(table, ntab, nvec, env);
+  p->shape = pick_shape(table, ntab, nvec, rows * D * static_cast<int64_t>(dtype_size(dtype)), env);
   p->two_phase = p->shape < 0;
   // Rows that need a cluster could also take the two-phase path (phase 2 then re-reads
   // from L2 when the problem is small).  Measured on B200 for [256, 65536] fp16 the two are
@@ -671,8 +682,13 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
   } else {
     snprintf(out, out_bytes, "rows tpr=%d vpt=%d cluster=%d rb=%d load=%s%d epv=%d block=%d grid=%d",
              p.rows.tpr, p.rows.vpt, p.rows.cluster, p.rows.rb,
-             p.rows.load_mode >= 2 ? "tma" : (p.rows.load_mode == 1 ? "prefetch" : "plain"),
-             p.rows.load_mode >= 2 ? p.rows.load_mode : 0, p.rows.epv, p.rows.block, p.rows.grid);
+             p.rows.load_mode >= 10 ? "tma-held"
+                                    : (p.rows.load_mode >= 2
+                                           ? "tma"
+                                           : (p.rows.load_mode == 1 ? "prefetch" : "plain")),
+             p.rows.load_mode >= 10 ? p.rows.load_mode - 10
+                                    : (p.rows.load_mode >= 2 ? p.rows.load_mode : 0),
+             p.rows.epv, p.rows.block, p.rows.grid);
   }
   return NVN_OK;
 }

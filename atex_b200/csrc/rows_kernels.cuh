@@ -57,6 +57,10 @@ struct RowBlock {
 //         >= 2: a shared-memory ring of PF stages filled by cp.async.bulk (TMA); one thread
 //         issues whole row batches, mbarriers signal arrival, and the bytes in flight no
 //         longer depend on registers or occupancy.
+//         >= 10 (backward only): a ring of PF - 10 stages whose row batch stays in shared
+//         memory until its dx has been written; both passes over the batch read it from
+//         there, so no fp32 copy of the batch lives in registers across the reduction and
+//         two CTAs of 256 threads fit on an SM.
 //
 // All element-wise math runs on fp32x2 lanes (nvn::P2) when EPV is even.
 
@@ -204,12 +208,14 @@ __device__ __forceinline__ void ring_tile(const unsigned char* stage, const unsi
 
 // After a bounded wait gave up: raise the status word and wait (bounded again) for the
 // copies that are still in flight, so none of them lands after the CTA has gone.
+// `ahead` = how many batches, counting batch j, have been issued and not yet waited for.
 template <typename Ring, int STAGES>
-__device__ __forceinline__ void ring_give_up(Ring& ring, int* status, int64_t j, int64_t nb) {
+__device__ __forceinline__ void ring_give_up(Ring& ring, int* status, int64_t j, int64_t nb,
+                                             int ahead = STAGES) {
   ring.dead = true;
   if (threadIdx.x == 0) {
     if (status != nullptr) atomicExch(status, 1);
-    const int64_t last = j + STAGES < nb ? j + STAGES : nb;
+    const int64_t last = j + ahead < nb ? j + ahead : nb;
     for (int64_t k = j; k < last; ++k)
       (void)mbar_wait_bounded(&ring.full[k % STAGES], static_cast<unsigned>(k / STAGES) & 1u);
   }
@@ -408,7 +414,9 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   constexpr int BLOCK = RowBlock<TPR, MINB>::kBlock;
   constexpr int RPC = RowBlock<TPR, MINB>::kRowsPerCta;
   constexpr bool TMA = PF >= 2;
-  constexpr int STAGES = TMA ? PF : 1;
+  constexpr bool HOLD = PF >= 10;
+  constexpr int STAGES = HOLD ? PF - 10 : (TMA ? PF : 1);
+  static_assert(!HOLD || STAGES >= 2, "a held ring needs a stage to refill while one is read");
   using Map = VecMap<TPR, VPT, CS, TMA>;
   constexpr int VSTRIDE = Map::kStride;
   static_assert(CS == 1 || RPC == 1, "cluster kernels own one row per cluster");
@@ -508,57 +516,122 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   load_stats(1, batch0 + stride + group);
   for (int64_t j = 0; j < nb; ++j) {
     const int64_t row0 = batch0 + j * stride + group;
+    const unsigned char* stage = nullptr;
     if constexpr (TMA) {
       const int s = static_cast<int>(j % STAGES);
       const bool ok = ring.wait(s, static_cast<unsigned>(j / STAGES));
-      ring_tile<T, EPV, VPT, RB, RPC, TPR, EXACT>(ring.stage_ptr(s), xoff, row0, N, nvalid, tx);
-      ring_tile<T, EPV, VPT, RB, RPC, TPR, EXACT>(ring.stage_ptr(s), dyoff, row0, N, nvalid, tdy);
-      if (__syncthreads_or(!ok) && !ring.dead) ring_give_up<decltype(ring), STAGES>(ring, a.status, j, nb);
-      if (tid == 0 && !ring.dead && j + STAGES < nb)
-        ring.issue(s, srcs, batch0 + (j + STAGES) * stride, N, D, crank);
+      stage = ring.stage_ptr(s);
+      if constexpr (!HOLD) {
+        ring_tile<T, EPV, VPT, RB, RPC, TPR, EXACT>(stage, xoff, row0, N, nvalid, tx);
+        ring_tile<T, EPV, VPT, RB, RPC, TPR, EXACT>(stage, dyoff, row0, N, nvalid, tdy);
+      }
+      if (__syncthreads_or(!ok) && !ring.dead)
+        ring_give_up<decltype(ring), STAGES>(ring, a.status, j, nb,
+                                             HOLD && j >= 1 ? STAGES - 1 : STAGES);
+      if constexpr (!HOLD) {
+        if (tid == 0 && !ring.dead && j + STAGES < nb)
+          ring.issue(s, srcs, batch0 + (j + STAGES) * stride, N, D, crank);
+      } else {
+        // Every thread is past the barrier above, hence past its last read of the previous
+        // batch: that batch's stage is free to be refilled.
+        if (tid == 0 && !ring.dead && j >= 1 && j - 1 + STAGES < nb)
+          ring.issue(static_cast<int>((j - 1) % STAGES), srcs, batch0 + (j - 1 + STAGES) * stride,
+                     N, D, crank);
+      }
     } else if constexpr (PF == 0) {
       load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, row0, N, rowvecs, nvalid, tx);
       load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(dyp, row0, N, rowvecs, nvalid, tdy);
     }
+    // Held ring: the batch's packed values come out of the stage, in both passes.
+    auto held = [&](int r, int v, P& px, P& pdy) {
+      if (row0 + r * RPC < N && (EXACT || v < nvalid)) {
+        px = reinterpret_cast<const P*>(stage + xoff[r])[v * TPR];
+        pdy = reinterpret_cast<const P*>(stage + dyoff[r])[v * TPR];
+      } else {
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) px.v[e] = pdy.v[e] = Cvt<T>::from_f32(0.f);
+      }
+    };
     float ivar[RB];
     load_stats(2, row0 + 2 * stride);
     // xh = (x - mean) * ivar ; gy = dy * gamma (LayerNorm) or dy (row-affine, where
     // gamma is a per-row scalar applied at the end).  red = (sum gy, sum gy * xh).
-    E xh[RB][VPT][NE], gy[RB][VPT][NE];
+    E xh[HOLD ? 1 : RB][HOLD ? 1 : VPT][NE], gy[HOLD ? 1 : RB][HOLD ? 1 : VPT][NE];
     float red[2 * RB];
+    float mean_of[HOLD ? RB : 1];
+    if constexpr (!HOLD) {
 #pragma unroll
-    for (int r = 0; r < RB; ++r) {
-      const float mean = st_mean[0][r];
-      ivar[r] = st_ivar[0][r];
-      const E nm = M::bcast(-mean), iv2 = M::bcast(ivar[r]);
-      E r0 = M::bcast(0.f), r1 = M::bcast(0.f);
+      for (int r = 0; r < RB; ++r) {
+        const float mean = st_mean[0][r];
+        ivar[r] = st_ivar[0][r];
+        const E nm = M::bcast(-mean), iv2 = M::bcast(ivar[r]);
+        E r0 = M::bcast(0.f), r1 = M::bcast(0.f);
 #pragma unroll
-      for (int v = 0; v < VPT; ++v) {
-        unpack<T, EPV>(tx.p[r][v], xh[r][v]);
-        unpack<T, EPV>(tdy.p[r][v], gy[r][v]);
-        if (EXACT || v < nvalid) {
-          E gg[NE];
-          if constexpr (!ROW_AFFINE && !PARAMS_IN_REGS)
-            load_param_lanes<EPV>(a.gamma, static_cast<int64_t>(vec0 + v * VSTRIDE) * EPV, gg);
+        for (int v = 0; v < VPT; ++v) {
+          unpack<T, EPV>(tx.p[r][v], xh[r][v]);
+          unpack<T, EPV>(tdy.p[r][v], gy[r][v]);
+          if (EXACT || v < nvalid) {
+            E gg[NE];
+            if constexpr (!ROW_AFFINE && !PARAMS_IN_REGS)
+              load_param_lanes<EPV>(a.gamma, static_cast<int64_t>(vec0 + v * VSTRIDE) * EPV, gg);
 #pragma unroll
-          for (int e = 0; e < NE; ++e) {
-            xh[r][v][e] = M::mul(M::add(xh[r][v][e], nm), iv2);
-            if constexpr (!ROW_AFFINE) {
-              dg[v][e] = M::fma(gy[r][v][e], xh[r][v][e], dg[v][e]);
-              db[v][e] = M::add(db[v][e], gy[r][v][e]);
-              if constexpr (PARAMS_IN_REGS) {
-                gy[r][v][e] = M::mul(gy[r][v][e], g[v][e]);
-              } else {
-                gy[r][v][e] = M::mul(gy[r][v][e], gg[e]);
+            for (int e = 0; e < NE; ++e) {
+              xh[r][v][e] = M::mul(M::add(xh[r][v][e], nm), iv2);
+              if constexpr (!ROW_AFFINE) {
+                dg[v][e] = M::fma(gy[r][v][e], xh[r][v][e], dg[v][e]);
+                db[v][e] = M::add(db[v][e], gy[r][v][e]);
+                if constexpr (PARAMS_IN_REGS) {
+                  gy[r][v][e] = M::mul(gy[r][v][e], g[v][e]);
+                } else {
+                  gy[r][v][e] = M::mul(gy[r][v][e], gg[e]);
+                }
               }
+              r0 = M::add(r0, gy[r][v][e]);
+              r1 = M::fma(gy[r][v][e], xh[r][v][e], r1);
             }
-            r0 = M::add(r0, gy[r][v][e]);
-            r1 = M::fma(gy[r][v][e], xh[r][v][e], r1);
           }
         }
+        red[2 * r] = M::hsum(r0);
+        red[2 * r + 1] = M::hsum(r1);
       }
-      red[2 * r] = M::hsum(r0);
-      red[2 * r + 1] = M::hsum(r1);
+    } else {
+#pragma unroll
+      for (int r = 0; r < RB; ++r) {
+        const float mean = mean_of[r] = st_mean[0][r];
+        ivar[r] = st_ivar[0][r];
+        const E nm = M::bcast(-mean), iv2 = M::bcast(ivar[r]);
+        E r0 = M::bcast(0.f), r1 = M::bcast(0.f);
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+          E xv[NE], gv[NE];
+          P px, pdy;
+          held(r, v, px, pdy);
+          unpack<T, EPV>(px, xv);
+          unpack<T, EPV>(pdy, gv);
+          if (EXACT || v < nvalid) {
+            E gg[NE];
+            if constexpr (!ROW_AFFINE && !PARAMS_IN_REGS)
+              load_param_lanes<EPV>(a.gamma, static_cast<int64_t>(vec0 + v * VSTRIDE) * EPV, gg);
+#pragma unroll
+            for (int e = 0; e < NE; ++e) {
+              xv[e] = M::mul(M::add(xv[e], nm), iv2);
+              if constexpr (!ROW_AFFINE) {
+                dg[v][e] = M::fma(gv[e], xv[e], dg[v][e]);
+                db[v][e] = M::add(db[v][e], gv[e]);
+                if constexpr (PARAMS_IN_REGS) {
+                  gv[e] = M::mul(gv[e], g[v][e]);
+                } else {
+                  gv[e] = M::mul(gv[e], gg[e]);
+                }
+              }
+              r0 = M::add(r0, gv[e]);
+              r1 = M::fma(gv[e], xv[e], r1);
+            }
+          }
+        }
+        red[2 * r] = M::hsum(r0);
+        red[2 * r + 1] = M::hsum(r1);
+      }
     }
 #pragma unroll
     for (int r = 0; r < RB; ++r) {
@@ -599,9 +672,33 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
         for (int v = 0; v < VPT; ++v) {
           if (EXACT || v < nvalid) {
             E o[NE];
+            if constexpr (HOLD) {
+              // second pass over the batch, again out of the ring stage
+              E xv[NE], gv[NE], gg[NE];
+              P px, pdy;
+              held(r, v, px, pdy);
+              unpack<T, EPV>(px, xv);
+              unpack<T, EPV>(pdy, gv);
+              if constexpr (!ROW_AFFINE && !PARAMS_IN_REGS)
+                load_param_lanes<EPV>(a.gamma, static_cast<int64_t>(vec0 + v * VSTRIDE) * EPV, gg);
+              const E nm = M::bcast(-mean_of[r]), iv2 = M::bcast(ivar[r]);
 #pragma unroll
-            for (int e = 0; e < NE; ++e)
-              o[e] = M::mul(M::add(gy[r][v][e], M::fma(xh[r][v][e], nm1, nm0)), sc2);
+              for (int e = 0; e < NE; ++e) {
+                xv[e] = M::mul(M::add(xv[e], nm), iv2);
+                if constexpr (!ROW_AFFINE) {
+                  if constexpr (PARAMS_IN_REGS) {
+                    gv[e] = M::mul(gv[e], g[v][e]);
+                  } else {
+                    gv[e] = M::mul(gv[e], gg[e]);
+                  }
+                }
+                o[e] = M::mul(M::add(gv[e], M::fma(xv[e], nm1, nm0)), sc2);
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < NE; ++e)
+                o[e] = M::mul(M::add(gy[r][v][e], M::fma(xh[r][v][e], nm1, nm0)), sc2);
+            }
             store_stream<T, EPV>(reinterpret_cast<T*>(rp + v * VSTRIDE), 0, repack<T, EPV>(o));
           }
         }
@@ -702,8 +799,11 @@ inline int resident_units(Kernel kernel, int block, int cs, size_t dyn_smem) {
   return clusters;
 }
 
-// Largest ring a TMA-mode kernel may ask for; wider problems use register prefetch.
+// Largest ring a TMA-mode kernel may ask for; wider problems use register prefetch.  Held
+// rings belong to shapes chosen so that the ring, not the register file, sets the number of
+// CTAs per SM, so they may take most of the SM's shared memory.
 constexpr size_t kMaxRingBytes = 96 * 1024;
+constexpr size_t kMaxHeldRingBytes = 200 * 1024;
 
 template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, int PF,
           bool EXACT, bool ROW_AFFINE, bool BWD>
@@ -715,12 +815,14 @@ inline cudaError_t launch_rows_exact(const RowsArgs& a, cudaStream_t stream, boo
   size_t ring = 0;
   if constexpr (TMA) {
     const size_t row_bytes = static_cast<size_t>(a.D / CS) * sizeof(T);
-    ring = row_bytes * (CS == 1 ? RPC * RB : RB) * (BWD ? 2 : 1) * PF;
+    ring = row_bytes * (CS == 1 ? RPC * RB : RB) * (BWD ? 2 : 1) * (PF >= 10 ? PF - 10 : PF);
     // rows that would need too large a ring, or clusters on rows that do not fill the
     // shape, fall back to the register-prefetch twin of this shape
-    if (ring > kMaxRingBytes || (CS > 1 && !EXACT) || sizeof(Pack<T, EPV>) < 16)
-      return launch_rows_exact<T, EPV, TPR, VPT, CS, RB, PR, MINB, 1, EXACT, ROW_AFFINE, BWD>(
-          a, stream, dry_run, plan);
+    if (ring > (PF >= 10 ? kMaxHeldRingBytes : kMaxRingBytes) || (CS > 1 && !EXACT) ||
+        sizeof(Pack<T, EPV>) < 16)
+      // (a held ring affords row batches that the register file does not)
+      return launch_rows_exact<T, EPV, TPR, VPT, CS, (PF >= 10 ? 1 : RB), PR, MINB, 1, EXACT,
+                               ROW_AFFINE, BWD>(a, stream, dry_run, plan);
   }
   void (*kernel)(const RowsArgs);
   if constexpr (BWD) {
@@ -746,8 +848,9 @@ inline cudaError_t launch_rows_exact(const RowsArgs& a, cudaStream_t stream, boo
       cudaError_t e = cudaFuncGetAttributes(&fa, kernel);
       if (e != cudaSuccess) return e;
       const size_t room = 227 * 1024 - fa.sharedSizeBytes - 1024;
+      const size_t most = PF >= 10 ? kMaxHeldRingBytes : kMaxRingBytes;
       e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(kMaxRingBytes < room ? kMaxRingBytes : room));
+                               static_cast<int>(most < room ? most : room));
       if (e != cudaSuccess) return e;
     }
     prepared.store(1, std::memory_order_release);
