@@ -12,6 +12,7 @@
 //
 // Replaces LayerNormGradBetaGammaTempToOut (atex/nv_norms/cc/kernels/
 // fused_layer_norm_op.cu:784-803) and ReduceNCtoC (fused_instance_norm_op.cu:442-457).
+#include "nvn_common.cuh"
 #include "nvn_host.h"
 
 namespace nvn {
@@ -27,6 +28,7 @@ __global__ void __launch_bounds__(kTX* TY)
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int64_t F2 = 2 * F;
   const int64_t col = (static_cast<int64_t>(blockIdx.x) * kTX + tx) * W;
+  griddep_wait();  // the partial rows come from the kernel launched just before
   float s[W];
 #pragma unroll
   for (int w = 0; w < W; ++w) s[w] = 0.f;
@@ -67,9 +69,10 @@ cudaError_t launch(const float* partials, int64_t P, int64_t F, float* dgamma, f
                    cudaStream_t s) {
   const int64_t blocks = (2 * F + kTX * W - 1) / (kTX * W);
   count_launch();
-  colreduce_kernel<TY, W><<<static_cast<unsigned>(blocks), dim3(kTX, TY), 0, s>>>(
-      partials, P, F, dgamma, dbeta);
-  return cudaGetLastError();
+  cudaLaunchAttribute attr;
+  const cudaLaunchConfig_t cfg =
+      dependent_launch_config(dim3(static_cast<unsigned>(blocks)), dim3(kTX, TY), 0, s, &attr);
+  return cudaLaunchKernelEx(&cfg, colreduce_kernel<TY, W>, partials, P, F, dgamma, dbeta);
 }
 }  // namespace
 

@@ -28,6 +28,7 @@
 // The reference has no communication at all (its ops are single-device); this stands
 // where a data-parallel TensorFlow job would run an all-reduce after the op.
 #include "../../include/nvnorms.h"
+#include "nvn_common.cuh"
 #include "nvn_host.h"
 
 namespace nvn {
@@ -69,6 +70,7 @@ __global__ void __launch_bounds__(kTX* TY)
   const int64_t col = (static_cast<int64_t>(blockIdx.x) * kTX + tx) * kW;
   const int64_t slot = static_cast<int64_t>(c.epoch & 3u) * c.world;
   if constexpr (PUSH) {
+  griddep_wait();  // the partial rows come from the kernel launched just before
   float s[kW] = {0.f, 0.f, 0.f, 0.f};
   if (col < F2) {
     for (int64_t p = ty; p < P; p += TY) {
@@ -140,6 +142,13 @@ cudaError_t launch(const float* partials, int64_t P, int64_t F, const DpPtrs& c,
                    float* dbeta, cudaStream_t s) {
   const int64_t blocks = (2 * F + kTX * kW - 1) / (kTX * kW);
   count_launch();
+  if constexpr (PUSH) {
+    cudaLaunchAttribute attr;
+    const cudaLaunchConfig_t cfg =
+        dependent_launch_config(dim3(static_cast<unsigned>(blocks)), dim3(kTX, TY), 0, s, &attr);
+    return cudaLaunchKernelEx(&cfg, colreduce_allreduce_kernel<TY, PUSH, FINISH>, partials, P, F,
+                              c, dgamma, dbeta);
+  }
   colreduce_allreduce_kernel<TY, PUSH, FINISH><<<static_cast<unsigned>(blocks), dim3(kTX, TY), 0, s>>>(
       partials, P, F, c, dgamma, dbeta);
   return cudaGetLastError();

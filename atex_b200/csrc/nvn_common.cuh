@@ -329,6 +329,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity
 }
 
 // ---------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-
+// serialization attribute may start while its predecessor in the stream still runs; it
+// must call griddep_wait() before touching anything the predecessor writes (the wait
+// returns once the predecessor has completed and its writes are visible).  The
+// predecessor calls griddep_launch_dependents() so that the dependent's CTAs are
+// scheduled as soon as SM resources free up.  Both are no-ops in launches without the
+// attribute.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;");
+}
+
+// ---------------------------------------------------------------------------
 // Row-group all-reduce (sum) of NV values.
 //
 // A "row group" is TPR consecutive threads of a CTA (TPR a power of two).  For

@@ -45,6 +45,23 @@ struct RowsPlan {
   int partial_rows;  // rows of [2][D] dgamma/dbeta partials the backward kernel writes
 };
 
+// Launch configuration for a kernel that follows the kernel it depends on in the same
+// stream and calls griddep_wait() (nvn_common.cuh) before reading that kernel's output:
+// its launch overlaps the predecessor's tail.  `attr` must outlive the launch call.
+inline cudaLaunchConfig_t dependent_launch_config(dim3 grid, dim3 block, size_t smem,
+                                                  cudaStream_t s, cudaLaunchAttribute* attr) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr->val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cfg;
+}
+
 int device_sm_count();
 void count_launch();
 // Device address of the library's status word on the current device (nullptr on failure).

@@ -428,6 +428,8 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   constexpr int NE = MathSel<EPV>::NE;
   using P = Pack<T, EPV>;
 
+  // The column reduction that follows may be scheduled as CTAs of this kernel retire.
+  griddep_launch_dependents();
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(8) uint64_t ring_bars[STAGES];
   __shared__ ReduceSmem<2 * RB, BLOCK> sm;
