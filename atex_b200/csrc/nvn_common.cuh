@@ -348,9 +348,9 @@ __device__ __forceinline__ void griddep_launch_dependents() {
 // A "row group" is TPR consecutive threads of a CTA (TPR a power of two).  For
 // TPR <= 32 the sum is a shuffle butterfly.  For TPR > 32 each warp's butterfly
 // result goes to shared memory and every thread adds the TPR/32 warp values in
-// index order.  With CS > 1 the CTA total is published in shared memory and
-// every CTA of the thread-block cluster adds the CS totals in rank order through
-// distributed shared memory.  The order of every addition is fixed, so the
+// index order.  With CS > 1 every CTA writes its total into all CTAs of the
+// thread-block cluster through distributed shared memory and every thread adds the
+// CS totals in rank order.  The order of every addition is fixed, so the
 // result is identical in all threads and from run to run.
 //
 // Shared-memory slots are double-buffered on `phase` (toggled by the caller
@@ -359,7 +359,7 @@ __device__ __forceinline__ void griddep_launch_dependents() {
 template <int NV, int BLOCK>
 struct ReduceSmem {
   float warp_part[2][NV][BLOCK / 32];
-  float cta_total[2][NV];
+  float cta_total[2][NV][16];  // [phase][value][cluster rank]; 16 = largest cluster
 };
 
 template <int NV, int TPR, int BLOCK, int CS>
@@ -389,20 +389,24 @@ __device__ __forceinline__ void group_allreduce(float (&v)[NV], ReduceSmem<NV, B
   }
   if constexpr (CS > 1) {
     static_assert(TPR == BLOCK, "a cluster shares one row, so the CTA is one row group");
+    static_assert(CS <= 16, "cta_total holds 16 ranks");
+    // Every CTA pushes its total into the slot of its rank in every CTA of the cluster
+    // (CS remote stores by CS lanes), then all threads read the CS totals from their own
+    // shared memory: far less distributed-shared-memory traffic than every thread
+    // fetching CS remote values.
     cg::cluster_group cluster = cg::this_cluster();
-    if (warp == 0 && lane == 0) {
+    const unsigned me = cluster.block_rank();
+    if (warp == 0 && lane < CS) {
 #pragma unroll
-      for (int k = 0; k < NV; ++k) sm.cta_total[phase][k] = v[k];
+      for (int k = 0; k < NV; ++k)
+        *cluster.map_shared_rank(&sm.cta_total[phase][k][me], lane) = v[k];
     }
     cluster.sync();
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       float s = 0.f;
 #pragma unroll
-      for (int r = 0; r < CS; ++r) {
-        const float* remote = cluster.map_shared_rank(&sm.cta_total[phase][k], r);
-        s += *remote;
-      }
+      for (int r = 0; r < CS; ++r) s += sm.cta_total[phase][k][r];
       v[k] = s;
     }
   }

@@ -84,7 +84,7 @@ int* device_status_word();
   X(0, 4, 1, 1, 4, 1, 0, 1)     X(1, 8, 1, 1, 4, 1, 0, 1)     X(2, 16, 1, 1, 4, 1, 0, 3)     \
   X(3, 32, 1, 1, 4, 1, 0, 3)    X(4, 32, 2, 1, 2, 1, 0, 3)    X(5, 32, 4, 1, 2, 1, 0, 3)     \
   X(6, 128, 2, 1, 1, 1, 0, 1)   X(7, 128, 4, 1, 1, 1, 0, 2)   X(8, 256, 4, 1, 1, 1, 0, 2)    \
-  X(9, 512, 4, 1, 1, 1, 0, 2)   X(10, 512, 8, 1, 1, 0, 0, 1)  X(11, 256, 8, 4, 1, 0, 0, 2)   \
+  X(9, 512, 4, 1, 1, 1, 0, 2)   X(10, 512, 8, 1, 1, 0, 0, 1)  X(11, 512, 4, 4, 1, 1, 0, 1)   \
   X(12, 512, 8, 4, 1, 0, 0, 1)  X(13, 512, 8, 8, 1, 0, 0, 1)  X(14, 512, 8, 16, 1, 0, 0, 1)  \
   /* three or five vectors per thread: widths of 3 * 2^k and 5 * 2^k elements */            \
   X(15, 32, 3, 1, 2, 1, 0, 3)   X(16, 64, 3, 1, 2, 1, 0, 3)   X(17, 128, 3, 1, 1, 1, 0, 2)   \
@@ -104,7 +104,7 @@ int* device_status_word();
   X(10, 256, 4, 1, 1, 1, 0, 12)    X(11, 512, 2, 1, 1, 1, 0, 1)                                \
   X(12, 512, 4, 1, 1, 1, 0, 12)    X(13, 512, 2, 2, 1, 1, 0, 1)                                \
   X(14, 128, 4, 8, 2, 1, 128, 12)  X(15, 512, 2, 4, 1, 1, 0, 1)                                \
-  X(16, 128, 4, 16, 2, 1, 128, 12) X(17, 256, 4, 8, 1, 1, 0, 1)                                \
+  X(16, 128, 4, 16, 2, 1, 128, 12) X(17, 512, 2, 8, 1, 1, 0, 1)                                \
   X(18, 512, 2, 16, 1, 1, 0, 1)    X(19, 512, 4, 16, 1, 0, 0, 1)                               \
   /* three or five vectors per thread: widths of 3 * 2^k and 5 * 2^k elements */            \
   X(20, 32, 3, 1, 2, 1, 128, 3)    X(21, 64, 3, 1, 2, 1, 128, 12)  X(22, 128, 3, 1, 1, 1, 128, 13) \

@@ -253,7 +253,12 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   const int group = tid / TPR;
   const int lir = tid % TPR;
   unsigned crank = 0;
-  if constexpr (CS > 1) crank = cg::this_cluster().block_rank();
+  if constexpr (CS > 1) {
+    crank = cg::this_cluster().block_rank();
+    // the reductions write into the peers' shared memory: every CTA of the cluster must
+    // have started before the first such write
+    cg::this_cluster().sync();
+  }
   const int64_t unit = blockIdx.x / CS;
   const int64_t nunits = gridDim.x / CS;
   const int64_t N = a.N;
@@ -442,7 +447,12 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   const int group = tid / TPR;
   const int lir = tid % TPR;
   unsigned crank = 0;
-  if constexpr (CS > 1) crank = cg::this_cluster().block_rank();
+  if constexpr (CS > 1) {
+    crank = cg::this_cluster().block_rank();
+    // the reductions write into the peers' shared memory: every CTA of the cluster must
+    // have started before the first such write
+    cg::this_cluster().sync();
+  }
   const int64_t unit = blockIdx.x / CS;
   const int64_t nunits = gridDim.x / CS;
   const int64_t N = a.N;
