@@ -36,9 +36,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 # DRAM traffic of one backward launch (dram__bytes_read + dram__bytes_write) taken from the
-# ncu capture summarised in profiles/rows_c2_ncu_full.md: 368.3 MB for 16384 rows of c2,
-# i.e. 22 478 bytes per row (traffic grows in proportion to the rows).  Only known for c2.
-NCU_BWD_TRAFFIC_BYTES_PER_ROW = {"c2": 368.3e6 / 16384}
+# ncu capture summarised in profiles/rows_c2_ncu_full.md: 370.9 MB for 16384 rows of c2,
+# i.e. 22 640 bytes per row (traffic grows in proportion to the rows).  Only known for c2.
+NCU_BWD_TRAFFIC_BYTES_PER_ROW = {"c2": 370.93e6 / 16384}
 
 NOMINAL_PEAK_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
