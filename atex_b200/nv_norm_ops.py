@@ -62,8 +62,10 @@ def _workspace(device: torch.device, nbytes: int) -> Tuple[int, int]:
 
 
 def _require(cond: bool, *msg) -> None:
+    """OP_REQUIRES: tensors among `msg` are rendered as their shape, and only on failure."""
     if not cond:
-        raise InvalidArgumentError("".join(str(m) for m in msg))
+        raise InvalidArgumentError("".join(
+            _shape_str(m) if isinstance(m, torch.Tensor) else str(m) for m in msg))
 
 
 def _check(status: int, what: str) -> None:
@@ -162,7 +164,7 @@ def fused_layer_norm_op(x, scale, offset, axis: Iterable[int] = (-1,), epsilon: 
     (the reference forwards its input buffer the same way).
     """
     _require(isinstance(x, torch.Tensor) and x.dim() > 0, "input must be at least 1-dimensional",
-             _shape_str(x) if isinstance(x, torch.Tensor) else "")
+             x if isinstance(x, torch.Tensor) else "")
     code = _dtype_code(x, "x")
     scale, offset = _param(scale, "scale"), _param(offset, "offset")
     axis = _axis_list(axis)
@@ -212,19 +214,19 @@ def fused_layer_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_spac
     `grad_exchange` (a sharding.GradExchange) the parameter gradients come back already
     summed over all data-parallel ranks."""
     _require(isinstance(y_backprop, torch.Tensor) and y_backprop.dim() > 0,
-             "input must be at least 1-dimensional", _shape_str(y_backprop))
+             "input must be at least 1-dimensional", y_backprop)
     _require(isinstance(x, torch.Tensor) and x.dim() > 0, "input must be at least 1-dimensional",
-             _shape_str(x))
+             x)
     dy = y_backprop
     code = _dtype_code(x, "x")
     if dy.dtype != x.dtype:
         raise TypeError(f"y_backprop ({dy.dtype}) and x ({x.dtype}) must have the same dtype")
     scale = _param(scale, "scale")
     mean, inv_std = _param(reserve_space_1, "reserve_space_1"), _param(reserve_space_2, "reserve_space_2")
-    _require(mean.dim() == 1, "saved mean must be 1-dimensional", _shape_str(mean))
-    _require(inv_std.dim() == 1, "saved inverted variance must be 1-dimensional", _shape_str(inv_std))
+    _require(mean.dim() == 1, "saved mean must be 1-dimensional", mean)
+    _require(inv_std.dim() == 1, "saved inverted variance must be 1-dimensional", inv_std)
     _require(x.shape == dy.shape, "x and y_backprop must have same shape, but x has shape ",
-             _shape_str(x), " and y_backprop has shape ", _shape_str(dy))
+             x, " and y_backprop has shape ", dy)
     N, D = _ln_dims(x, _axis_list(axis))
     _require(scale.numel() == D, "scale must have the same number of elements as the features "
              "of x, got ", scale.numel(), " and ", D)
@@ -261,8 +263,8 @@ def fused_instance_norm_op(x, scale, offset, data_format: str = "N...C", epsilon
     N, C, D, cf = _in_dims(x, data_format)
     code = _dtype_code(x, "x")
     scale, offset = _param(scale, "scale"), _param(offset, "offset")
-    _require(scale.dim() == 1, "scale must be 1-dimensional", _shape_str(scale))
-    _require(offset.dim() == 1, "offset must be 1-dimensional", _shape_str(offset))
+    _require(scale.dim() == 1, "scale must be 1-dimensional", scale)
+    _require(offset.dim() == 1, "offset must be 1-dimensional", offset)
     _require(scale.numel() == C, "scale must have the same number of elements as the channels "
              "of x, got ", scale.numel(), " and ", C)
     _require(offset.numel() == C, "offset must have the same number of elements as the channels "
@@ -292,20 +294,20 @@ def fused_instance_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_s
     """FusedInstanceNormGrad (norm_ops.cc:189-202): returns (x_backprop, scale_backprop,
     offset_backprop).  `out_grads` optionally supplies the two parameter-gradient buffers."""
     _require(isinstance(y_backprop, torch.Tensor) and y_backprop.dim() > 3,
-             "input must be at least 4-dimensional", _shape_str(y_backprop))
+             "input must be at least 4-dimensional", y_backprop)
     _require(isinstance(x, torch.Tensor) and x.dim() > 1, "input must be at least 2-dimensional",
-             _shape_str(x))
+             x)
     dy = y_backprop
     code = _dtype_code(x, "x")
     if dy.dtype != x.dtype:
         raise TypeError(f"y_backprop ({dy.dtype}) and x ({x.dtype}) must have the same dtype")
     scale = _param(scale, "scale")
     mean, inv_std = _param(reserve_space_1, "reserve_space_1"), _param(reserve_space_2, "reserve_space_2")
-    _require(scale.dim() == 1, "scale must be 1-dimensional", _shape_str(scale))
-    _require(mean.dim() == 2, "saved mean must be 2-dimensional", _shape_str(mean))
-    _require(inv_std.dim() == 2, "saved inverted variance must be 2-dimensional", _shape_str(inv_std))
+    _require(scale.dim() == 1, "scale must be 1-dimensional", scale)
+    _require(mean.dim() == 2, "saved mean must be 2-dimensional", mean)
+    _require(inv_std.dim() == 2, "saved inverted variance must be 2-dimensional", inv_std)
     _require(x.shape == dy.shape, "x and y_backprop must have same shape, but x has shape ",
-             _shape_str(x), " and y_backprop has shape ", _shape_str(dy))
+             x, " and y_backprop has shape ", dy)
     N, C, D, cf = _in_dims(x, data_format)
     _require(scale.numel() == C, "scale must have the same number of elements as the channels "
              "of x, got ", scale.numel(), " and ", C)
