@@ -43,6 +43,7 @@ def _units():
     units.append(("twophase.o", "twophase.cu", []))
     units.append(("colreduce.o", "colreduce.cu", []))
     units.append(("colreduce_dp.o", "colreduce_dp.cu", []))
+    units.append(("colslice.o", "colslice.cu", []))
     units.append(("nvnorms_api.o", "nvnorms_api.cu", []))
     extra = os.path.join(CSRC, "noalloc.cu")
     if os.path.exists(extra):

@@ -45,6 +45,20 @@ struct RowsPlan {
   int partial_rows;  // rows of [2][D] dgamma/dbeta partials the backward kernel writes
 };
 
+// Column-sliced LayerNorm kernels for wide rows (colslice.cu): every CTA owns 4 * vpl
+// vectors of every row; per-row partial sums meet behind a grid barrier.
+struct ColslicePlan {
+  int vpl;               // lanes that share a row slice (4 vectors per lane)
+  int grid;              // CTAs = column slices
+  size_t partial_bytes;  // [rows][grid] float2
+};
+bool colslice_plan(int64_t nvec, int64_t rows, ColslicePlan* p);
+// Backward writes the final dgamma / dbeta.  `partials` holds plan.partial_bytes, `counter`
+// one 32-bit word (zeroed by the launch itself).
+cudaError_t colslice_launch(int dtype, bool bwd, const ColslicePlan& p, const RowsArgs& r,
+                            float* dgamma, float* dbeta, void* partials, void* counter,
+                            cudaStream_t s);
+
 // Launch configuration for a kernel that follows the kernel it depends on in the same
 // stream and calls griddep_wait() (nvn_common.cuh) before reading that kernel's output:
 // its launch overlaps the predecessor's tail.  `attr` must outlive the launch call.
@@ -81,9 +95,9 @@ int* device_status_word();
 // first entry (in listing order) among those of the smallest sufficient capacity.
 #ifndef NVN_ROW_SHAPES_LIGHT
 #define NVN_ROW_SHAPES_LIGHT(X)                                                              \
-  X(0, 4, 1, 1, 4, 1, 0, 1)     X(1, 8, 1, 1, 4, 1, 0, 1)     X(2, 16, 1, 1, 4, 1, 0, 3)     \
+  X(0, 4, 1, 1, 4, 1, 0, 1)     X(1, 8, 1, 1, 4, 1, 0, 1)     X(2, 8, 2, 1, 4, 1, 0, 3)      \
   X(3, 32, 1, 1, 4, 1, 0, 3)    X(4, 32, 2, 1, 2, 1, 0, 3)    X(5, 32, 4, 1, 2, 1, 0, 3)     \
-  X(6, 128, 2, 1, 1, 1, 0, 1)   X(7, 128, 4, 1, 1, 1, 0, 2)   X(8, 256, 4, 1, 1, 1, 0, 2)    \
+  X(6, 128, 2, 1, 1, 1, 128, 1)  X(7, 128, 4, 1, 1, 1, 0, 2)   X(8, 256, 4, 1, 1, 1, 0, 2)    \
   X(9, 512, 4, 1, 1, 1, 0, 2)   X(10, 512, 8, 1, 1, 0, 0, 1)  X(11, 512, 4, 4, 1, 1, 0, 1)   \
   X(12, 512, 8, 4, 1, 0, 0, 1)  X(13, 512, 8, 8, 1, 0, 0, 1)  X(14, 512, 8, 16, 1, 0, 0, 1)  \
   /* three or five vectors per thread: widths of 3 * 2^k and 5 * 2^k elements */            \

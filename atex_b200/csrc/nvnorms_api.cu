@@ -123,6 +123,9 @@ int fail_cuda(cudaError_t e) {
 // ---------------------------------------------------------------------------
 struct RowProblemPlan {
   bool two_phase;
+  bool colslice;   // wide LayerNorm rows: column-sliced kernels behind a grid barrier
+  ColslicePlan cs;
+  size_t off_cs_part, off_cs_counter;
   bool scalar;     // two-phase variant runs element-wise
   int epv;         // elements per access of the row-cached variant
   int shape;       // row-cached variant
@@ -157,6 +160,28 @@ int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int
     if (v != nullptr && v[0] == 't') p->two_phase = true;
   }
   size_t off = 0;
+  // Experimental: LayerNorm rows of more than 2048 vectors cut by columns instead of rows
+  // (colslice.cu).  Correct, but on B200 still slower than the cluster shapes
+  // ([256, 65536] fp16: 35 + 49 us against 25 + 36 us), so it only runs on request
+  // (NVN_WIDE_ROWS=colslice).
+  if (!row_affine && full && nvec > 2048 && !p->two_phase) {
+    const char* v = getenv("NVN_WIDE_ROWS");
+    if (v != nullptr && v[0] == 'c' && v[1] == 'o' && colslice_plan(nvec, rows, &p->cs)) {
+      p->colslice = true;
+      p->off_cs_part = off;
+      off += align_up(p->cs.partial_bytes, 256);
+      p->off_cs_counter = off;
+      off += 256;
+      if (bwd) {
+        // one row of [dgamma | dbeta] for the data-parallel exchange to pick up
+        p->colpart_rows = 1;
+        p->off_colpart = off;
+        off += align_up(static_cast<size_t>(2) * D * 4, 256);
+      }
+      p->bytes = off;
+      return NVN_OK;
+    }
+  }
   if (!p->two_phase) {
     RowsArgs a = {};
     a.N = rows;
@@ -217,6 +242,35 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
   char* wsb = static_cast<char*>(ws);
   const int64_t F = row_affine ? C : D;
 
+  if (p.colslice) {
+    RowsArgs a = {};
+    a.x = x;
+    a.dy = dy;
+    a.gamma = gamma;
+    a.beta = beta;
+    a.mean_in = mean_in;
+    a.ivar_in = ivar_in;
+    a.out = out;
+    a.mean = mean;
+    a.ivar = ivar;
+    a.N = rows;
+    a.D = D;
+    a.C = C;
+    a.eps = eps;
+    a.status = device_status_word();
+    // alone, the kernel writes dgamma / dbeta itself; with a data-parallel exchange they go
+    // to the workspace as the single partial row the exchange kernel sums and sends
+    float* colpart = bwd ? reinterpret_cast<float*>(wsb + p.off_colpart) : nullptr;
+    cudaError_t e = colslice_launch(dtype, bwd, p.cs, a, comm != nullptr ? colpart : dgamma,
+                                    comm != nullptr ? colpart + D : dbeta, wsb + p.off_cs_part,
+                                    wsb + p.off_cs_counter, stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+    if (bwd && comm != nullptr) {
+      e = colreduce_allreduce_launch(colpart, 1, F, comm, dgamma, dbeta, stream);
+      if (e != cudaSuccess) return fail_cuda(e);
+    }
+    return NVN_OK;
+  }
   if (!p.two_phase) {
     RowsArgs a = {};
     a.x = x;
@@ -675,7 +729,10 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
   RowProblemPlan p;
   int st = plan_rows(dtype, bwd, is_in, rows, D, N, is_in ? C : 1, 16, 16, &p);
   if (st != NVN_OK) return st;
-  if (p.two_phase) {
+  if (p.colslice) {
+    snprintf(out, out_bytes, "colslice lanes=%d vpl=4 epv=%d grid=%d", p.cs.vpl, p.epv,
+             p.cs.grid);
+  } else if (p.two_phase) {
     snprintf(out, out_bytes, "rows two-phase epv=%d chunk=%lld nchunks=%d slices=%d",
              p.scalar ? 1 : full_epv(dtype), static_cast<long long>(p.r2.chunk), p.r2.nchunks,
              p.r2.slices);
