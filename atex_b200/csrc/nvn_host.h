@@ -59,6 +59,16 @@ cudaError_t colslice_launch(int dtype, bool bwd, const ColslicePlan& p, const Ro
                             float* dgamma, float* dbeta, void* partials, void* counter,
                             cudaStream_t s);
 
+// On-chip channels-last InstanceNorm (nlc_onchip.cu): one CTA holds a whole batch item in
+// shared memory.  nlc_onchip_ok: the item fits and C / vector divides the CTA size.  The
+// backward launch leaves per-item (dgamma, dbeta) contributions in colpart[N][2][C].
+bool nlc_onchip_ok(int dtype, bool bwd, int64_t C, int64_t D);
+cudaError_t nlc_onchip_launch(int dtype, bool bwd, const void* dy, const void* x,
+                              const float* gamma, const float* beta, const float* mean_in,
+                              const float* ivar_in, int64_t N, int64_t C, int64_t D, float eps,
+                              void* out, float* mean, float* ivar, float* colpart, int* status,
+                              cudaStream_t s);
+
 // Launch configuration for a kernel that follows the kernel it depends on in the same
 // stream and calls griddep_wait() (nvn_common.cuh) before reading that kernel's output:
 // its launch overlaps the predecessor's tail.  `attr` must outlive the launch call.

@@ -328,14 +328,25 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
 // ---------------------------------------------------------------------------
 struct NlcPlan {
   bool scalar;
+  bool onchip;  // a batch item fits in shared memory: one launch, one pass over HBM
   S2Plan s2;
   size_t off_part, off_coef, off_colpart, bytes;
 };
 
-int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, NlcPlan* p) {
+int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, NlcPlan* p,
+             bool allow_onchip = true) {
   memset(p, 0, sizeof(*p));
   const int V = full_epv(dtype);
   p->scalar = !(vec_ok && C % V == 0);
+  if (vec_ok && allow_onchip && nlc_onchip_ok(dtype, bwd, C, D)) {
+    const char* v = getenv("NVN_NLC");  // NVN_NLC=twophase keeps the two-phase kernels
+    if (!(v != nullptr && v[0] == 't')) {
+      p->onchip = true;
+      p->off_colpart = 0;
+      p->bytes = bwd ? align_up(static_cast<size_t>(N) * 2 * C * 4, 256) : 0;
+      return NVN_OK;
+    }
+  }
   const int epv = p->scalar ? 1 : V;
   if (N > 65535) return NVN_ERR_UNSUPPORTED;
   p->s2 = s2_plan(dtype, bwd, N, C, D, epv);
@@ -359,11 +370,27 @@ int run_nlc(int dtype, bool bwd, const void* dy, const void* x, const float* gam
             float* dbeta, void* ws, size_t ws_bytes, cudaStream_t stream,
             const nvn_dp_comm* comm = nullptr) {
   bool vec_ok = aligned(x, 16) && aligned(out, 16) && (!bwd || aligned(dy, 16));
+  // the on-chip kernels also read the parameters and the saved statistics as vectors
+  const bool par_ok = aligned(gamma, 16) && (bwd ? aligned(mean_in, 16) && aligned(ivar_in, 16)
+                                                 : aligned(beta, 16));
   NlcPlan p;
-  int st = plan_nlc(dtype, bwd, N, C, D, vec_ok, &p);
+  int st = plan_nlc(dtype, bwd, N, C, D, vec_ok, &p, par_ok);
   if (st != NVN_OK) return st;
-  if (ws == nullptr || !aligned(ws, 256) || ws_bytes < p.bytes) return NVN_ERR_WORKSPACE;
+  if (p.bytes > 0 && (ws == nullptr || !aligned(ws, 256) || ws_bytes < p.bytes))
+    return NVN_ERR_WORKSPACE;
   char* wsb = static_cast<char*>(ws);
+  if (p.onchip) {
+    float* colpart = bwd ? reinterpret_cast<float*>(wsb + p.off_colpart) : nullptr;
+    cudaError_t e = nlc_onchip_launch(dtype, bwd, dy, x, gamma, beta, mean_in, ivar_in, N, C, D,
+                                      eps, out, mean, ivar, colpart, device_status_word(), stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+    if (bwd) {
+      e = comm != nullptr ? colreduce_allreduce_launch(colpart, N, C, comm, dgamma, dbeta, stream)
+                          : colreduce_launch(colpart, N, C, dgamma, dbeta, stream);
+      if (e != cudaSuccess) return fail_cuda(e);
+    }
+    return NVN_OK;
+  }
   S2Args a = {};
   a.x = x;
   a.dy = dy;
@@ -719,6 +746,10 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
     NlcPlan p;
     int st = plan_nlc(dtype, bwd, N, C, D, true, &p);
     if (st != NVN_OK) return st;
+    if (p.onchip) {
+      snprintf(out, out_bytes, "nlc on-chip epv=%d block=256", full_epv(dtype));
+      return NVN_OK;
+    }
     snprintf(out, out_bytes,
              "nlc two-phase epv=%d cvt=%d lanes=%d ctiles=%d chunk=%lld nchunks=%d group=%d",
              p.scalar ? 1 : full_epv(dtype), p.s2.cvt, p.s2.lanes, p.s2.ctiles,

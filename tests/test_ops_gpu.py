@@ -153,6 +153,32 @@ def test_instance_norm_channel_counts(dtype, channel_first, N, C, spatial):
     check_in(x, dy, g, b, 1e-5, channel_first)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,C,spatial,fwd_on_chip,bwd_on_chip", [
+    (700, 32, (4, 4), True, True),        # more items than resident CTAs: the persistent loop
+    (5, 64, (16, 16), True, True),
+    (3, 512, (8, 8), True, False),        # x + dy of one item exceed the backward slab
+    (4, 16, (8, 8, 8), True, True),
+    (2, 24, (8, 8), False, False),        # 3 channel vectors do not divide the CTA
+])
+def test_channels_last_items_that_fit_run_on_chip(lib, dtype, N, C, spatial, fwd_on_chip, bwd_on_chip):
+    """N...C items that fit in shared memory take the one-launch on-chip kernels (bulk copy of
+    the whole item, per-channel sums over the threads that share a channel vector)."""
+    code = {"f32": _lib.NVN_F32, "f16": _lib.NVN_F16, "bf16": _lib.NVN_BF16}[dtype]
+    D = int(np.prod(spatial))
+    es = 4 if dtype == "f32" else 2
+    vec = 16 // es
+    fits = lambda tensors: D * C * es * tensors <= 88 * 1024
+    divides = C % vec == 0 and C <= 512 and 256 % (C // vec) == 0
+    for op, want, tensors in ((2, fwd_on_chip, 1), (3, bwd_on_chip, 2)):
+        plan = _lib.describe_plan(op, code, N, C, D, 0)
+        expect = want and divides and fits(tensors)
+        assert plan.startswith("nlc on-chip") == expect, (plan, expect)
+    x, dy, g, b = rand_in(N, C, spatial, False, dtype, seed=N + C)
+    check_in(x, dy, g, b, 1e-3, False)
+    assert lib.nvn_device_status() == _lib.NVN_OK
+
+
 def test_empty_inputs_launch_nothing_and_zero_the_param_grads():
     # fused_layer_norm_test.py:153-179, fused_instance_norm_test.py:181-214
     g = torch.ones(8, device=DEV)
