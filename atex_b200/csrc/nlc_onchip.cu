@@ -7,9 +7,9 @@
 // exactly once, in one launch.  Thread t owns the 128-bit vectors t, t + 256, ... of the item;
 // because the channel vectors per voxel (C / EPV) divide the CTA size, all of a thread's
 // vectors belong to the same EPV channels, so gamma / beta and the statistics of those
-// channels live in registers.  Per-channel sums go through a [256][EPV] shared-memory array:
-// every thread deposits its partial sums, then channel c is summed over the 256 * EPV / C
-// threads that hold it, in thread order (fixed order => bit-identical from run to run).
+// channels live in registers.  Per-channel sums: xor shuffles over the lanes of a warp that
+// share a channel vector, one deposit per warp and channel in shared memory, then a sum over
+// the warps in a fixed order (=> bit-identical from run to run).
 // Forward statistics are exact two-pass (mean, then centred squares).
 //
 // Replaces InstanceNormBlockSMemChnlLastImpl (atex/nv_norms/cc/kernels/
@@ -54,21 +54,57 @@ struct NlcOnchipArgs {
   int* status;
 };
 
-// Sum, per channel, of the per-thread partials in red[256][EPV]; the result for channel c
-// lands in tot[c].  Threads cooperate: thread t handles channels t, t + 256, ...
+// Per-channel sum over the CTA of every thread's EPV partial sums `acc`; the total of channel
+// c lands in tot[c] (valid after the trailing barrier).  `scratch` holds kBlock * EPV floats.
+// The cv threads-per-voxel pattern repeats inside a warp when cv <= 16, so the lanes that
+// share a channel vector are first summed with xor shuffles; each warp then deposits one
+// value per channel and channel c is summed over the warps (or, for cv >= 32, over the
+// kBlock / cv threads that hold it), always in the same order.
 template <int EPV>
-__device__ __forceinline__ void channel_totals(const float (*red)[EPV], float* tot, int C, int cv) {
-  const int holders = kBlock / cv;  // threads that hold a given channel vector
-  for (int c = threadIdx.x; c < C; c += kBlock) {
-    const int v = c / EPV, e = c % EPV;
-    float s = 0.f;
-    for (int k = 0; k < holders; ++k) s += red[v + cv * k][e];
-    tot[c] = s;
+__device__ __forceinline__ void channel_totals(
+    typename MathSel<EPV>::M::E (&acc)[MathSel<EPV>::NE], float* scratch, float* tot, int C,
+    int cv) {
+  using M = typename MathSel<EPV>::M;
+  constexpr int NE = MathSel<EPV>::NE;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  if (cv <= 32) {
+    for (int off = 16; off >= cv; off >>= 1) {
+#pragma unroll
+      for (int e = 0; e < NE; ++e) {
+        if constexpr (EPV == 1) {
+          acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
+        } else {
+          acc[e].x += __shfl_xor_sync(0xffffffffu, acc[e].x, off);
+          acc[e].y += __shfl_xor_sync(0xffffffffu, acc[e].y, off);
+        }
+      }
+    }
+    if (lane < cv) store_param_lanes<EPV>(scratch + warp * C + lane * EPV, 0, acc);
+    __syncthreads();
+    for (int c = t; c < C; c += kBlock) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < kBlock / 32; ++w) s += scratch[w * C + c];
+      tot[c] = s;
+    }
+  } else {
+    store_param_lanes<EPV>(scratch + t * EPV, 0, acc);
+    __syncthreads();
+    const int holders = kBlock / cv;
+    for (int c = t; c < C; c += kBlock) {
+      const int v = c / EPV, e = c % EPV;
+      float s = 0.f;
+      for (int k = 0; k < holders; ++k) s += scratch[(v + cv * k) * EPV + e];
+      tot[c] = s;
+    }
   }
+  __syncthreads();
 }
 
-template <typename T, bool BWD>
-__global__ void __launch_bounds__(kBlock) nlc_onchip_kernel(const NlcOnchipArgs a) {
+// STAGES = 2: the next item is copied into the other half of the slab while this one is
+// processed (items of at most half the slab budget); STAGES = 1: one item at a time.
+template <typename T, bool BWD, int STAGES>
+__global__ void __launch_bounds__(kBlock, BWD ? 2 : 3) nlc_onchip_kernel(const NlcOnchipArgs a) {
   constexpr int EPV = VecTraits<T>::kFull;
   using M = typename MathSel<EPV>::M;
   using E = typename M::E;
@@ -76,8 +112,8 @@ __global__ void __launch_bounds__(kBlock) nlc_onchip_kernel(const NlcOnchipArgs 
   using P = Pack<T, EPV>;
   constexpr int NT = BWD ? 2 : 1;
 
-  extern __shared__ __align__(128) unsigned char slab[];  // [NT][item bytes]
-  __shared__ __align__(8) uint64_t bar;
+  extern __shared__ __align__(128) unsigned char slab_mem[];  // [STAGES][NT][item bytes]
+  __shared__ __align__(8) uint64_t bars[STAGES];
   __shared__ __align__(16) float red[NT][kBlock][EPV];
   __shared__ __align__(16) float tot[2][kMaxChannels];
 
@@ -89,8 +125,7 @@ __global__ void __launch_bounds__(kBlock) nlc_onchip_kernel(const NlcOnchipArgs 
   const int nvec = static_cast<int>(item_elems / EPV);
   const unsigned item_bytes = static_cast<unsigned>(item_elems * sizeof(T));
   const float inv_D = 1.0f / static_cast<float>(a.D);
-  const P* sx = reinterpret_cast<const P*>(slab);
-  const P* sdy = reinterpret_cast<const P*>(slab + item_bytes);
+  const unsigned stage_bytes = item_bytes * NT;
 
   // parameters of this thread's EPV channels
   E g[NE], be[NE];
@@ -98,25 +133,42 @@ __global__ void __launch_bounds__(kBlock) nlc_onchip_kernel(const NlcOnchipArgs 
   if constexpr (!BWD) load_param_lanes<EPV>(a.beta, static_cast<int64_t>(my_cv) * EPV, be);
 
   if (t == 0) {
-    mbar_init(&bar, 1);
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
     mbar_init_fence();
   }
   __syncthreads();
   bool dead = false;  // a bounded wait gave up: stop copying and waiting, finish the loop
+  auto issue = [&](int64_t n, int stage) {
+    unsigned char* dst = slab_mem + static_cast<size_t>(stage) * stage_bytes;
+    mbar_expect_tx(&bars[stage], stage_bytes);
+    bulk_load(dst, static_cast<const T*>(a.x) + n * item_elems, item_bytes, &bars[stage]);
+    if constexpr (BWD)
+      bulk_load(dst + item_bytes, static_cast<const T*>(a.dy) + n * item_elems, item_bytes,
+                &bars[stage]);
+  };
+  if (STAGES == 2 && t == 0 && blockIdx.x < a.N) issue(blockIdx.x, 0);
 
   unsigned use = 0;
   for (int64_t n = blockIdx.x; n < a.N; n += gridDim.x, ++use) {
+    const int stage = STAGES == 2 ? static_cast<int>(use & 1u) : 0;
     if (t == 0 && !dead) {
-      mbar_expect_tx(&bar, item_bytes * NT);
-      bulk_load(slab, static_cast<const T*>(a.x) + n * item_elems, item_bytes, &bar);
-      if constexpr (BWD)
-        bulk_load(slab + item_bytes, static_cast<const T*>(a.dy) + n * item_elems, item_bytes, &bar);
+      if constexpr (STAGES == 2) {
+        // the other stage was released by the barrier that ended the previous iteration
+        if (n + gridDim.x < a.N) issue(n + gridDim.x, stage ^ 1);
+      } else {
+        issue(n, 0);
+      }
     }
-    const bool ok = dead ? true : mbar_wait_bounded(&bar, use & 1u);
+    const unsigned parity = STAGES == 2 ? ((use >> 1) & 1u) : (use & 1u);
+    const bool ok = dead ? true : mbar_wait_bounded(&bars[stage], parity);
     if (__syncthreads_or(!ok) && !dead) {
       dead = true;
       if (t == 0 && a.status != nullptr) atomicExch(a.status, 1);
     }
+    const P* sx = reinterpret_cast<const P*>(slab_mem + static_cast<size_t>(stage) * stage_bytes);
+    const P* sdy = reinterpret_cast<const P*>(slab_mem + static_cast<size_t>(stage) * stage_bytes +
+                                              item_bytes);
 
     if constexpr (!BWD) {
       // pass 1: per-channel sums
@@ -129,10 +181,7 @@ __global__ void __launch_bounds__(kBlock) nlc_onchip_kernel(const NlcOnchipArgs 
 #pragma unroll
         for (int e = 0; e < NE; ++e) acc[e] = M::add(acc[e], xe[e]);
       }
-      store_param_lanes<EPV>(&red[0][t][0], 0, acc);
-      __syncthreads();
-      channel_totals<EPV>(red[0], tot[0], C, cv);
-      __syncthreads();
+      channel_totals<EPV>(acc, &red[0][0][0], tot[0], C, cv);
       E mean[NE];
       lanes_from_smem<EPV>(&tot[0][my_cv * EPV], mean);
 #pragma unroll
@@ -149,10 +198,7 @@ __global__ void __launch_bounds__(kBlock) nlc_onchip_kernel(const NlcOnchipArgs 
           acc[e] = M::fma(d, d, acc[e]);
         }
       }
-      store_param_lanes<EPV>(&red[0][t][0], 0, acc);
-      __syncthreads();
-      channel_totals<EPV>(red[0], tot[1], C, cv);
-      __syncthreads();
+      channel_totals<EPV>(acc, &red[0][0][0], tot[1], C, cv);
       // per-channel results: inverse std in tot[1], outputs to global
       for (int c = t; c < C; c += kBlock) {
         const float m = tot[0][c] * inv_D;
@@ -197,12 +243,8 @@ __global__ void __launch_bounds__(kBlock) nlc_onchip_kernel(const NlcOnchipArgs 
           s2[e] = M::fma(de[e], xh, s2[e]);
         }
       }
-      store_param_lanes<EPV>(&red[0][t][0], 0, s1);
-      store_param_lanes<EPV>(&red[1][t][0], 0, s2);
-      __syncthreads();
-      channel_totals<EPV>(red[0], tot[0], C, cv);
-      channel_totals<EPV>(red[1], tot[1], C, cv);
-      __syncthreads();
+      channel_totals<EPV>(s1, &red[0][0][0], tot[0], C, cv);
+      channel_totals<EPV>(s2, &red[1][0][0], tot[1], C, cv);
       // per-item contributions to dgamma (sum dy * xhat) and dbeta (sum dy): [n][2][C]
       for (int c = t; c < C; c += kBlock) {
         a.colpart[(n * 2 + 0) * C + c] = tot[1][c];
@@ -236,27 +278,38 @@ __global__ void __launch_bounds__(kBlock) nlc_onchip_kernel(const NlcOnchipArgs 
   }
 }
 
-template <typename T, bool BWD>
-cudaError_t launch_t(NlcOnchipArgs& a, size_t slab_bytes, cudaStream_t s) {
-  auto kernel = nlc_onchip_kernel<T, BWD>;
+template <typename T, bool BWD, int STAGES>
+cudaError_t launch_s(NlcOnchipArgs& a, size_t slab_bytes, cudaStream_t s) {
+  auto kernel = nlc_onchip_kernel<T, BWD, STAGES>;
+  const size_t smem = slab_bytes * STAGES;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(slab_bytes));
+                                       static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   int per_sm = 0;
-  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kBlock, slab_bytes);
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kBlock, smem);
   if (e != cudaSuccess) return e;
   if (per_sm < 1) per_sm = 1;
   const int64_t resident = static_cast<int64_t>(device_sm_count()) * per_sm;
   const unsigned grid = static_cast<unsigned>(a.N < resident ? a.N : resident);
   count_launch();
-  kernel<<<grid, kBlock, slab_bytes, s>>>(a);
+  kernel<<<grid, kBlock, smem, s>>>(a);
   return cudaGetLastError();
+}
+
+constexpr size_t kSlabBudget = 88 * 1024;  // two CTAs per SM
+
+template <typename T, bool BWD>
+cudaError_t launch_t(NlcOnchipArgs& a, size_t slab_bytes, cudaStream_t s) {
+  // two stages when both fit the budget and there is a next item to prefetch
+  if (2 * slab_bytes <= kSlabBudget && a.N > device_sm_count())
+    return launch_s<T, BWD, 2>(a, slab_bytes, s);
+  return launch_s<T, BWD, 1>(a, slab_bytes, s);
 }
 
 }  // namespace
 
 // Items of at most this many bytes (x, plus dy in the backward pass) are handled on chip.
-constexpr size_t kNlcOnchipMaxSlab = 88 * 1024;  // two CTAs per SM
+constexpr size_t kNlcOnchipMaxSlab = kSlabBudget;
 
 bool nlc_onchip_ok(int dtype, bool bwd, int64_t C, int64_t D) {
   const int epv = dtype == 0 ? 4 : 8;
