@@ -19,11 +19,14 @@
 #include "nvn_common.cuh"
 #include "nvn_host.h"
 
+#include <atomic>
+
 namespace nvn {
 
 namespace {
 
 constexpr int kBlock = 256;
+constexpr size_t kSlabBudget = 88 * 1024;  // dynamic shared memory per CTA: two CTAs per SM
 constexpr int kMaxChannels = 512;  // bounds the per-channel arrays in shared memory
 
 // EPV consecutive floats of a shared-memory array as math lanes
@@ -282,21 +285,32 @@ template <typename T, bool BWD, int STAGES>
 cudaError_t launch_s(NlcOnchipArgs& a, size_t slab_bytes, cudaStream_t s) {
   auto kernel = nlc_onchip_kernel<T, BWD, STAGES>;
   const size_t smem = slab_bytes * STAGES;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem));
-  if (e != cudaSuccess) return e;
+  // Per process and kernel: the opt-in to large dynamic shared memory, and the occupancy for
+  // the last slab size seen (every device this library runs on is the same part).
+  static std::atomic<int> prepared{0};
+  static std::atomic<int64_t> cached{0};  // (smem << 8) | CTAs per SM
+  if (prepared.load(std::memory_order_acquire) == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kSlabBudget));
+    if (e != cudaSuccess) return e;
+    prepared.store(1, std::memory_order_release);
+  }
   int per_sm = 0;
-  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kBlock, smem);
-  if (e != cudaSuccess) return e;
-  if (per_sm < 1) per_sm = 1;
+  const int64_t c = cached.load(std::memory_order_relaxed);
+  if (c != 0 && static_cast<size_t>(c >> 8) == smem) {
+    per_sm = static_cast<int>(c & 0xff);
+  } else {
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kBlock, smem);
+    if (e != cudaSuccess) return e;
+    if (per_sm < 1) per_sm = 1;
+    cached.store((static_cast<int64_t>(smem) << 8) | per_sm, std::memory_order_relaxed);
+  }
   const int64_t resident = static_cast<int64_t>(device_sm_count()) * per_sm;
   const unsigned grid = static_cast<unsigned>(a.N < resident ? a.N : resident);
   count_launch();
   kernel<<<grid, kBlock, smem, s>>>(a);
   return cudaGetLastError();
 }
-
-constexpr size_t kSlabBudget = 88 * 1024;  // two CTAs per SM
 
 template <typename T, bool BWD>
 cudaError_t launch_t(NlcOnchipArgs& a, size_t slab_bytes, cudaStream_t s) {
