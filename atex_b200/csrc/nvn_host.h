@@ -135,6 +135,17 @@ int* device_status_word();
   X(23, 128, 5, 1, 1, 1, 128, 12)  X(24, 256, 3, 1, 1, 1, 0, 12)   X(25, 512, 3, 1, 1, 1, 0, 12)
 #endif
 
+// InstanceNorm "NC..." backward for rows of more than 2048 vectors.  The light table's wide
+// shapes hold 8 vectors per thread, which the backward kernel (x-hat and dy of the batch in
+// registers across the reduction) cannot afford at 512 threads; these shapes keep at most 4
+// vectors per thread or hold the batch in the ring.  Indices start at 256; wider rows take
+// the two-phase kernels.
+#ifndef NVN_ROW_SHAPES_AFFINE_WIDE
+#define NVN_ROW_SHAPES_AFFINE_WIDE(X)                                                        \
+  X(256, 256, 4, 4, 1, 0, 0, 1)    X(257, 512, 4, 4, 1, 0, 0, 1)
+#endif
+constexpr int kAffineWideBase = 256;
+
 // Rows accessed with less than 128 bits per access (64-, 32-bit or single elements: widths
 // that are not a multiple of the vector, misaligned buffers) share this coarser table.
 #define NVN_ROW_SHAPES_SCALAR(X)                                                             \

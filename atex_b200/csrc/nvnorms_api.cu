@@ -35,10 +35,12 @@ struct Shape {
 const Shape kLightShapes[] = {NVN_ROW_SHAPES_LIGHT(X)};
 const Shape kHeavyShapes[] = {NVN_ROW_SHAPES_HEAVY(X)};
 const Shape kScalarShapes[] = {NVN_ROW_SHAPES_SCALAR(X)};
+const Shape kAffineWideShapes[] = {NVN_ROW_SHAPES_AFFINE_WIDE(X)};
 #undef X
 constexpr int kNumLight = sizeof(kLightShapes) / sizeof(Shape);
 constexpr int kNumHeavy = sizeof(kHeavyShapes) / sizeof(Shape);
 constexpr int kNumScalar = sizeof(kScalarShapes) / sizeof(Shape);
+constexpr int kNumAffineWide = sizeof(kAffineWideShapes) / sizeof(Shape);
 
 inline int64_t cap(const Shape& s) { return static_cast<int64_t>(s.tpr) * s.vpt * s.cs; }
 
@@ -146,16 +148,24 @@ int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int
   const bool full = epv == V;
   const int64_t nvec = D / epv;
   const bool heavy = bwd && !row_affine;
-  const Shape* table = !full ? kScalarShapes : (heavy ? kHeavyShapes : kLightShapes);
-  const int ntab = !full ? kNumScalar : (heavy ? kNumHeavy : kNumLight);
-  const char* env = !full ? nullptr : (bwd ? "NVN_FORCE_BWD_SHAPE" : "NVN_FORCE_FWD_SHAPE");
+  // InstanceNorm backward on rows of more than 2048 vectors has a table of its own
+  const bool affine_wide = bwd && row_affine && full && nvec > 2048;
+  const Shape* table = !full ? kScalarShapes
+                             : (heavy ? kHeavyShapes : (affine_wide ? kAffineWideShapes : kLightShapes));
+  const int ntab =
+      !full ? kNumScalar : (heavy ? kNumHeavy : (affine_wide ? kNumAffineWide : kNumLight));
+  const char* env = !full ? nullptr
+                          : (affine_wide ? "NVN_FORCE_AFFINE_SHAPE"
+                                         : (bwd ? "NVN_FORCE_BWD_SHAPE" : "NVN_FORCE_FWD_SHAPE"));
   p->shape = pick_shape(table, ntab, nvec, rows * D * static_cast<int64_t>(dtype_size(dtype)), env);
   p->two_phase = p->shape < 0;
+  const int table_index = p->shape;  // `table[table_index]` below; p->shape is what the launcher gets
+  if (affine_wide && p->shape >= 0) p->shape += kAffineWideBase;
   // Rows that need a cluster could also take the two-phase path (phase 2 then re-reads
   // from L2 when the problem is small).  Measured on B200 for [256, 65536] fp16 the two are
   // equal (70 us fwd+bwd), so the single-launch cluster kernel stays the default;
   // NVN_WIDE_ROWS=twophase switches for experiments.
-  if (!p->two_phase && table[p->shape].cs > 1) {
+  if (!p->two_phase && table[table_index].cs > 1) {
     const char* v = getenv("NVN_WIDE_ROWS");
     if (v != nullptr && v[0] == 't') p->two_phase = true;
   }

@@ -934,6 +934,13 @@ cudaError_t launch_rows_vec(int shape, const RowsArgs& a, cudaStream_t s, bool d
       default:
         return cudaErrorInvalidValue;
     }
+  } else if constexpr (BWD && ROW_AFFINE) {
+    switch (shape) {
+      NVN_ROW_SHAPES_LIGHT(X)
+      NVN_ROW_SHAPES_AFFINE_WIDE(X)
+      default:
+        return cudaErrorInvalidValue;
+    }
   } else {
     switch (shape) {
       NVN_ROW_SHAPES_LIGHT(X)
