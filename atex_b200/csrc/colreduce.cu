@@ -23,17 +23,21 @@ constexpr int kTX = 32;
 template <int TY, int W>  // W columns per thread: 4 (float4) or 1
 __global__ void __launch_bounds__(kTX* TY)
     colreduce_kernel(const float* __restrict__ partials, int64_t P, int64_t F,
-                     float* __restrict__ dgamma, float* __restrict__ dbeta) {
+                     float* __restrict__ dgamma, float* __restrict__ dbeta,
+                     int64_t slab_rows, float* __restrict__ slab_out) {
   __shared__ float tile[TY][kTX * W + 1];
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int64_t F2 = 2 * F;
   const int64_t col = (static_cast<int64_t>(blockIdx.x) * kTX + tx) * W;
+  // blockIdx.y selects a slab of rows (a single slab covers all rows)
+  const int64_t p_begin = static_cast<int64_t>(blockIdx.y) * slab_rows;
+  const int64_t p_end = p_begin + slab_rows < P ? p_begin + slab_rows : P;
   griddep_wait();  // the partial rows come from the kernel launched just before
   float s[W];
 #pragma unroll
   for (int w = 0; w < W; ++w) s[w] = 0.f;
   if (col < F2) {
-    for (int64_t p = ty; p < P; p += TY) {
+    for (int64_t p = p_begin + ty; p < p_end; p += TY) {
       if constexpr (W == 4) {
         const float4 v = *reinterpret_cast<const float4*>(partials + p * F2 + col);
         s[0] += v.x;
@@ -55,7 +59,9 @@ __global__ void __launch_bounds__(kTX* TY)
 #pragma unroll
       for (int k = 0; k < TY; ++k) t += tile[k][tx * W + w];
       const int64_t c = col + w;
-      if (c < F) {
+      if (slab_out != nullptr) {
+        slab_out[static_cast<int64_t>(blockIdx.y) * F2 + c] = t;
+      } else if (c < F) {
         dgamma[c] = t;
       } else {
         dbeta[c - F] = t;
@@ -66,19 +72,37 @@ __global__ void __launch_bounds__(kTX* TY)
 
 template <int TY, int W>
 cudaError_t launch(const float* partials, int64_t P, int64_t F, float* dgamma, float* dbeta,
-                   cudaStream_t s) {
+                   cudaStream_t s, int64_t slabs = 1, float* slab_out = nullptr) {
   const int64_t blocks = (2 * F + kTX * W - 1) / (kTX * W);
+  const int64_t slab_rows = (P + slabs - 1) / slabs;
   count_launch();
   cudaLaunchAttribute attr;
-  const cudaLaunchConfig_t cfg =
-      dependent_launch_config(dim3(static_cast<unsigned>(blocks)), dim3(kTX, TY), 0, s, &attr);
-  return cudaLaunchKernelEx(&cfg, colreduce_kernel<TY, W>, partials, P, F, dgamma, dbeta);
+  const cudaLaunchConfig_t cfg = dependent_launch_config(
+      dim3(static_cast<unsigned>(blocks), static_cast<unsigned>(slabs)), dim3(kTX, TY), 0, s, &attr);
+  return cudaLaunchKernelEx(&cfg, colreduce_kernel<TY, W>, partials, P, F, dgamma, dbeta,
+                            slab_rows, slab_out);
 }
 }  // namespace
 
+// With few columns and very many partial rows (InstanceNorm over a large batch: one partial
+// row per item) the column tiles alone give a handful of CTAs.  Given scratch for
+// `scratch_rows` rows of [2F], the rows are then cut into slabs that are reduced side by side
+// and a second launch sums the slab results; the order of the additions stays fixed.
 cudaError_t colreduce_launch(const float* partials, int64_t P, int64_t F, float* dgamma,
-                             float* dbeta, cudaStream_t s) {
+                             float* dbeta, cudaStream_t s, float* scratch, int64_t scratch_rows) {
   const bool vec = (2 * F) % 4 == 0 && (reinterpret_cast<uintptr_t>(partials) & 15) == 0;
+  const int64_t col_blocks = (2 * F + kTX * (vec ? 4 : 1) - 1) / (kTX * (vec ? 4 : 1));
+  if (scratch != nullptr && scratch_rows >= 2 && P >= 4096 && col_blocks < 64) {
+    int64_t slabs = P / 1024;  // at least 1024 rows per slab
+    if (slabs > scratch_rows) slabs = scratch_rows;
+    if (slabs * col_blocks > 1024) slabs = 1024 / col_blocks;
+    if (slabs >= 2) {
+      const cudaError_t e = vec ? launch<32, 4>(partials, P, F, dgamma, dbeta, s, slabs, scratch)
+                                : launch<32, 1>(partials, P, F, dgamma, dbeta, s, slabs, scratch);
+      if (e != cudaSuccess) return e;
+      return colreduce_launch(scratch, slabs, F, dgamma, dbeta, s, nullptr, 0);
+    }
+  }
   if (vec) {
     if (P <= 4) return launch<1, 4>(partials, P, F, dgamma, dbeta, s);
     if (P <= 32) return launch<4, 4>(partials, P, F, dgamma, dbeta, s);

@@ -149,7 +149,7 @@ constexpr int kAffineWideBase = 256;
 // Rows accessed with less than 128 bits per access (64-, 32-bit or single elements: widths
 // that are not a multiple of the vector, misaligned buffers) share this coarser table.
 #define NVN_ROW_SHAPES_SCALAR(X)                                                             \
-  X(0, 8, 4, 1, 2, 0, 0, 1) X(1, 32, 8, 1, 2, 0, 0, 1) X(2, 256, 8, 1, 1, 0, 0, 1)           \
+  X(0, 8, 4, 1, 2, 0, 0, 1) X(1, 32, 8, 1, 1, 0, 0, 1) X(2, 256, 8, 1, 1, 0, 0, 1)           \
   X(3, 512, 8, 2, 1, 0, 0, 1) X(4, 512, 8, 8, 1, 0, 0, 1) X(5, 512, 8, 16, 1, 0, 0, 1)
 
 // One entry point per (dtype, direction) translation unit.  `epv` (elements per access: the
@@ -168,8 +168,12 @@ NVN_DECLARE_ROWS(rows_bf16_bwd)
 
 // Deterministic second stage of the dgamma / dbeta reduction: sums P partial
 // rows of [2][F] floats (dgamma then dbeta) in a fixed order.
+// `scratch` (optional, `scratch_rows` rows of [2F] floats, 16-byte aligned) lets the kernel
+// split very many partial rows into slabs when there are few columns.
+constexpr int64_t kColreduceScratchRows = 256;
 cudaError_t colreduce_launch(const float* partials, int64_t P, int64_t F, float* dgamma,
-                             float* dbeta, cudaStream_t s);
+                             float* dbeta, cudaStream_t s, float* scratch = nullptr,
+                             int64_t scratch_rows = 0);
 
 // Column reduction fused with the all-reduce over peer memory (colreduce_dp.cu).  Needs
 // 2F % 4 == 0.

@@ -78,6 +78,13 @@ inline bool aligned(const void* p, size_t a) {
   return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
 }
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+// Scratch the column reduction may use to split very many partial rows of F features into
+// slabs (colreduce.cu); only InstanceNorm over thousands of items gets there.
+inline size_t colreduce_scratch_bytes(int64_t partial_rows, int64_t F) {
+  return partial_rows >= 4096
+             ? align_up(static_cast<size_t>(kColreduceScratchRows) * 2 * F * 4, 256)
+             : 0;
+}
 inline size_t dtype_size(int dtype) { return dtype == NVN_F32 ? 4 : 2; }
 inline int full_epv(int dtype) { return dtype == NVN_F32 ? 4 : 8; }
 
@@ -125,6 +132,8 @@ int fail_cuda(cudaError_t e) {
 // ---------------------------------------------------------------------------
 struct RowProblemPlan {
   bool two_phase;
+  size_t off_colscratch;  // slab scratch of the column reduction (0 bytes: none)
+  bool has_colscratch;
   bool colslice;   // wide LayerNorm rows: column-sliced kernels behind a grid barrier
   ColslicePlan cs;
   size_t off_cs_part, off_cs_counter;
@@ -219,6 +228,12 @@ int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int
       p->off_colpart = off;
       off += align_up(static_cast<size_t>(p->colpart_rows) * 2 * (row_affine ? C : D) * 4, 256);
     }
+  }
+  if (bwd) {
+    const size_t sb = colreduce_scratch_bytes(p->colpart_rows, row_affine ? C : D);
+    p->has_colscratch = sb > 0;
+    p->off_colscratch = off;
+    off += sb;
   }
   p->bytes = off;
   return NVN_OK;
@@ -326,8 +341,12 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
     const float* partials = reinterpret_cast<const float*>(wsb + p.off_colpart);
     cudaError_t e = comm != nullptr ? colreduce_allreduce_launch(partials, p.colpart_rows, F, comm,
                                                                  dgamma, dbeta, stream)
-                                    : colreduce_launch(partials, p.colpart_rows, F, dgamma, dbeta,
-                                                       stream);
+                                    : colreduce_launch(
+                                          partials, p.colpart_rows, F, dgamma, dbeta, stream,
+                                          p.has_colscratch
+                                              ? reinterpret_cast<float*>(wsb + p.off_colscratch)
+                                              : nullptr,
+                                          p.has_colscratch ? kColreduceScratchRows : 0);
     if (e != cudaSuccess) return fail_cuda(e);
   }
   return NVN_OK;
@@ -340,7 +359,8 @@ struct NlcPlan {
   bool scalar;
   bool onchip;  // a batch item fits in shared memory: one launch, one pass over HBM
   S2Plan s2;
-  size_t off_part, off_coef, off_colpart, bytes;
+  size_t off_part, off_coef, off_colpart, off_colscratch, bytes;
+  bool has_colscratch;
 };
 
 int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, NlcPlan* p,
@@ -354,11 +374,16 @@ int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, 
       p->onchip = true;
       p->off_colpart = 0;
       p->bytes = bwd ? align_up(static_cast<size_t>(N) * 2 * C * 4, 256) : 0;
+      if (bwd) {
+        const size_t sb = colreduce_scratch_bytes(N, C);
+        p->has_colscratch = sb > 0;
+        p->off_colscratch = p->bytes;
+        p->bytes += sb;
+      }
       return NVN_OK;
     }
   }
   const int epv = p->scalar ? 1 : V;
-  if (N > 65535) return NVN_ERR_UNSUPPORTED;
   p->s2 = s2_plan(dtype, bwd, N, C, D, epv);
   if (p->s2.ctiles > 65535) return NVN_ERR_UNSUPPORTED;
   size_t off = 0;
@@ -369,6 +394,10 @@ int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, 
     off += align_up(static_cast<size_t>(N) * 3 * C * 4, 256);
     p->off_colpart = off;
     off += align_up(static_cast<size_t>(N) * 2 * C * 4, 256);
+    const size_t sb = colreduce_scratch_bytes(N, C);
+    p->has_colscratch = sb > 0;
+    p->off_colscratch = off;
+    off += sb;
   }
   p->bytes = off;
   return NVN_OK;
@@ -396,7 +425,11 @@ int run_nlc(int dtype, bool bwd, const void* dy, const void* x, const float* gam
     if (e != cudaSuccess) return fail_cuda(e);
     if (bwd) {
       e = comm != nullptr ? colreduce_allreduce_launch(colpart, N, C, comm, dgamma, dbeta, stream)
-                          : colreduce_launch(colpart, N, C, dgamma, dbeta, stream);
+                          : colreduce_launch(colpart, N, C, dgamma, dbeta, stream,
+                                             p.has_colscratch
+                                                 ? reinterpret_cast<float*>(wsb + p.off_colscratch)
+                                                 : nullptr,
+                                             p.has_colscratch ? kColreduceScratchRows : 0);
       if (e != cudaSuccess) return fail_cuda(e);
     }
     return NVN_OK;
@@ -421,7 +454,10 @@ int run_nlc(int dtype, bool bwd, const void* dy, const void* x, const float* gam
   if (bwd) {
     e = comm != nullptr
             ? colreduce_allreduce_launch(a.ws_colpart, N, C, comm, dgamma, dbeta, stream)
-            : colreduce_launch(a.ws_colpart, N, C, dgamma, dbeta, stream);
+            : colreduce_launch(a.ws_colpart, N, C, dgamma, dbeta, stream,
+                               p.has_colscratch ? reinterpret_cast<float*>(wsb + p.off_colscratch)
+                                                : nullptr,
+                               p.has_colscratch ? kColreduceScratchRows : 0);
     if (e != cudaSuccess) return fail_cuda(e);
   }
   return NVN_OK;

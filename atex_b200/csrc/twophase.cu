@@ -1059,7 +1059,7 @@ S2Plan s2_plan(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, int epv) {
   // walks items and chunks in reverse, which keeps the tail of phase 1 an L2 hit.
   (void)dtype;
   (void)bwd;
-  const int64_t group = N;
+  const int64_t group = N < 65535 ? N : 65535;  // grid.z counts the items of a group
   p.group = static_cast<int>(group);
   // voxels one CTA sweep covers
   const int64_t sweep = static_cast<int64_t>(p.lanes) * kUnroll;

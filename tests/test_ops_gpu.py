@@ -179,6 +179,17 @@ def test_channels_last_items_that_fit_run_on_chip(lib, dtype, N, C, spatial, fwd
     assert lib.nvn_device_status() == _lib.NVN_OK
 
 
+@pytest.mark.parametrize("channel_first", [True, False])
+@pytest.mark.parametrize("N,C,spatial", [(9000, 3, (4, 4)), (70000, 3, (2, 2)), (5000, 8, (2, 4))])
+def test_instance_norm_over_many_items(lib, channel_first, N, C, spatial):
+    """Thousands of batch items: the parameter-gradient reduction runs over one partial row per
+    item (split into slabs when there are few channels), and the channels-last two-phase
+    kernels launch in groups of at most 65535 items."""
+    x, dy, g, b = rand_in(N, C, spatial, channel_first, "f16", seed=N + C)
+    check_in(x, dy, g, b, 1e-3, channel_first)
+    assert lib.nvn_device_status() == _lib.NVN_OK
+
+
 def test_empty_inputs_launch_nothing_and_zero_the_param_grads():
     # fused_layer_norm_test.py:153-179, fused_instance_norm_test.py:181-214
     g = torch.ones(8, device=DEV)
