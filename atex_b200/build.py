@@ -45,6 +45,7 @@ def _units():
     units.append(("colreduce_dp.o", "colreduce_dp.cu", []))
     units.append(("colslice.o", "colslice.cu", []))
     units.append(("nlc_onchip.o", "nlc_onchip.cu", []))
+    units.append(("nlc_small.o", "nlc_small.cu", []))
     units.append(("nvnorms_api.o", "nvnorms_api.cu", []))
     extra = os.path.join(CSRC, "noalloc.cu")
     if os.path.exists(extra):

@@ -69,6 +69,14 @@ cudaError_t nlc_onchip_launch(int dtype, bool bwd, const void* dy, const void* x
                               void* out, float* mean, float* ivar, float* colpart, int* status,
                               cudaStream_t s);
 
+// Warp-per-item channels-last InstanceNorm for small items (nlc_small.cu): any dtype, C and
+// alignment, C <= 32 and D * C <= 4096 elements.  Backward leaves colpart[N][2][C].
+bool nlc_small_ok(int64_t C, int64_t D);
+cudaError_t nlc_small_launch(int dtype, bool bwd, const void* dy, const void* x,
+                             const float* gamma, const float* beta, const float* mean_in,
+                             const float* ivar_in, int64_t N, int64_t C, int64_t D, float eps,
+                             void* out, float* mean, float* ivar, float* colpart, cudaStream_t s);
+
 // Launch configuration for a kernel that follows the kernel it depends on in the same
 // stream and calls griddep_wait() (nvn_common.cuh) before reading that kernel's output:
 // its launch overlaps the predecessor's tail.  `attr` must outlive the launch call.

@@ -358,6 +358,7 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
 struct NlcPlan {
   bool scalar;
   bool onchip;  // a batch item fits in shared memory: one launch, one pass over HBM
+  bool small;   // small items: one warp per item
   S2Plan s2;
   size_t off_part, off_coef, off_colpart, off_colscratch, bytes;
   bool has_colscratch;
@@ -368,7 +369,25 @@ int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, 
   memset(p, 0, sizeof(*p));
   const int V = full_epv(dtype);
   p->scalar = !(vec_ok && C % V == 0);
-  if (vec_ok && allow_onchip && nlc_onchip_ok(dtype, bwd, C, D)) {
+  // Small items: a warp per item beats a CTA per item below 2048 elements, and is the only
+  // one-launch path for channel counts or alignments the vector kernels cannot take.
+  const bool onchip_ok = vec_ok && allow_onchip && nlc_onchip_ok(dtype, bwd, C, D);
+  if (nlc_small_ok(C, D) && (D * C <= 2048 || !onchip_ok)) {
+    const char* v = getenv("NVN_NLC");
+    if (!(v != nullptr && (v[0] == 't' || v[0] == 'o'))) {
+      p->small = true;
+      p->off_colpart = 0;
+      p->bytes = bwd ? align_up(static_cast<size_t>(N) * 2 * C * 4, 256) : 0;
+      if (bwd) {
+        const size_t sb = colreduce_scratch_bytes(N, C);
+        p->has_colscratch = sb > 0;
+        p->off_colscratch = p->bytes;
+        p->bytes += sb;
+      }
+      return NVN_OK;
+    }
+  }
+  if (onchip_ok) {
     const char* v = getenv("NVN_NLC");  // NVN_NLC=twophase keeps the two-phase kernels
     if (!(v != nullptr && v[0] == 't')) {
       p->onchip = true;
@@ -418,9 +437,12 @@ int run_nlc(int dtype, bool bwd, const void* dy, const void* x, const float* gam
   if (p.bytes > 0 && (ws == nullptr || !aligned(ws, 256) || ws_bytes < p.bytes))
     return NVN_ERR_WORKSPACE;
   char* wsb = static_cast<char*>(ws);
-  if (p.onchip) {
+  if (p.onchip || p.small) {
     float* colpart = bwd ? reinterpret_cast<float*>(wsb + p.off_colpart) : nullptr;
-    cudaError_t e = nlc_onchip_launch(dtype, bwd, dy, x, gamma, beta, mean_in, ivar_in, N, C, D,
+    cudaError_t e = p.small
+                        ? nlc_small_launch(dtype, bwd, dy, x, gamma, beta, mean_in, ivar_in, N, C,
+                                           D, eps, out, mean, ivar, colpart, stream)
+                        : nlc_onchip_launch(dtype, bwd, dy, x, gamma, beta, mean_in, ivar_in, N, C, D,
                                       eps, out, mean, ivar, colpart, device_status_word(), stream);
     if (e != cudaSuccess) return fail_cuda(e);
     if (bwd) {
@@ -635,8 +657,11 @@ static size_t in_workspace_bytes(int dtype, bool bwd, int64_t N, int64_t C, int6
     return rows_workspace_bytes(dtype, bwd, true, N * C, D, N, C);
   NlcPlan pv, ps;
   size_t b = 0;
-  if (plan_nlc(dtype, bwd, N, C, D, true, &pv) == NVN_OK) b = pv.bytes;
-  if (plan_nlc(dtype, bwd, N, C, D, false, &ps) == NVN_OK) b = std::max(b, ps.bytes);
+  // whichever path alignment lets the call take, the workspace must be large enough
+  for (const bool vec_ok : {true, false})
+    for (const bool onchip : {true, false})
+      if (plan_nlc(dtype, bwd, N, C, D, vec_ok, &pv, onchip) == NVN_OK) b = std::max(b, pv.bytes);
+  (void)ps;
   return b;
 }
 
@@ -792,6 +817,10 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
     NlcPlan p;
     int st = plan_nlc(dtype, bwd, N, C, D, true, &p);
     if (st != NVN_OK) return st;
+    if (p.small) {
+      snprintf(out, out_bytes, "nlc warp-per-item block=256");
+      return NVN_OK;
+    }
     if (p.onchip) {
       snprintf(out, out_bytes, "nlc on-chip epv=%d block=256", full_epv(dtype));
       return NVN_OK;

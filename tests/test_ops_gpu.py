@@ -155,7 +155,8 @@ def test_instance_norm_channel_counts(dtype, channel_first, N, C, spatial):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("N,C,spatial,fwd_on_chip,bwd_on_chip", [
-    (700, 32, (4, 4), True, True),        # more items than resident CTAs: the persistent loop
+    (700, 32, (4, 4), True, True),        # small enough for a warp per item
+    (700, 32, (8, 16), True, True),       # more items than resident CTAs: the persistent loop
     (5, 64, (16, 16), True, True),
     (3, 512, (8, 8), True, False),        # x + dy of one item exceed the backward slab
     (4, 16, (8, 8, 8), True, True),
@@ -170,10 +171,12 @@ def test_channels_last_items_that_fit_run_on_chip(lib, dtype, N, C, spatial, fwd
     vec = 16 // es
     fits = lambda tensors: D * C * es * tensors <= 88 * 1024
     divides = C % vec == 0 and C <= 512 and 256 % (C // vec) == 0
+    small = C <= 32 and D * C <= 2048   # these go to the warp-per-item kernels instead
     for op, want, tensors in ((2, fwd_on_chip, 1), (3, bwd_on_chip, 2)):
         plan = _lib.describe_plan(op, code, N, C, D, 0)
-        expect = want and divides and fits(tensors)
+        expect = want and divides and fits(tensors) and not small
         assert plan.startswith("nlc on-chip") == expect, (plan, expect)
+        assert plan.startswith("nlc warp-per-item") == small, plan
     x, dy, g, b = rand_in(N, C, spatial, False, dtype, seed=N + C)
     check_in(x, dy, g, b, 1e-3, False)
     assert lib.nvn_device_status() == _lib.NVN_OK
