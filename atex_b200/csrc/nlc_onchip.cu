@@ -26,7 +26,8 @@ namespace nvn {
 namespace {
 
 constexpr int kBlock = 256;
-constexpr size_t kSlabBudget = 88 * 1024;  // dynamic shared memory per CTA: two CTAs per SM
+constexpr size_t kSlabBudget = 88 * 1024;  // dynamic shared memory per CTA for two CTAs per SM
+constexpr size_t kSlabMax = 192 * 1024;    // largest slab: one CTA per SM
 constexpr int kMaxChannels = 512;  // bounds the per-channel arrays in shared memory
 
 // EPV consecutive floats of a shared-memory array as math lanes
@@ -291,7 +292,7 @@ cudaError_t launch_s(NlcOnchipArgs& a, size_t slab_bytes, cudaStream_t s) {
   static std::atomic<int64_t> cached{0};  // (smem << 8) | CTAs per SM
   if (prepared.load(std::memory_order_acquire) == 0) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kSlabBudget));
+                                         static_cast<int>(kSlabMax));
     if (e != cudaSuccess) return e;
     prepared.store(1, std::memory_order_release);
   }
@@ -323,7 +324,7 @@ cudaError_t launch_t(NlcOnchipArgs& a, size_t slab_bytes, cudaStream_t s) {
 }  // namespace
 
 // Items of at most this many bytes (x, plus dy in the backward pass) are handled on chip.
-constexpr size_t kNlcOnchipMaxSlab = kSlabBudget;
+constexpr size_t kNlcOnchipMaxSlab = kSlabMax;
 
 bool nlc_onchip_ok(int dtype, bool bwd, int64_t C, int64_t D) {
   const int epv = dtype == 0 ? 4 : 8;

@@ -158,7 +158,8 @@ def test_instance_norm_channel_counts(dtype, channel_first, N, C, spatial):
     (700, 32, (4, 4), True, True),        # small enough for a warp per item
     (700, 32, (8, 16), True, True),       # more items than resident CTAs: the persistent loop
     (5, 64, (16, 16), True, True),
-    (3, 512, (8, 8), True, False),        # x + dy of one item exceed the backward slab
+    (3, 512, (8, 8), True, True),         # 64 KB items: one CTA per SM in the backward pass
+    (2, 256, (32, 32), False, False),     # 512 KB (fp16) items exceed the slab
     (4, 16, (8, 8, 8), True, True),
     (2, 24, (8, 8), False, False),        # 3 channel vectors do not divide the CTA
 ])
@@ -169,7 +170,7 @@ def test_channels_last_items_that_fit_run_on_chip(lib, dtype, N, C, spatial, fwd
     D = int(np.prod(spatial))
     es = 4 if dtype == "f32" else 2
     vec = 16 // es
-    fits = lambda tensors: D * C * es * tensors <= 88 * 1024
+    fits = lambda tensors: D * C * es * tensors <= 192 * 1024
     divides = C % vec == 0 and C <= 512 and 256 % (C // vec) == 0
     small = C <= 32 and D * C <= 2048   # these go to the warp-per-item kernels instead
     for op, want, tensors in ((2, fwd_on_chip, 1), (3, bwd_on_chip, 2)):
