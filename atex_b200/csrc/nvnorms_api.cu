@@ -174,6 +174,14 @@ int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int
   // from L2 when the problem is small).  Measured on B200 for [256, 65536] fp16 the two are
   // equal (70 us fwd+bwd), so the single-launch cluster kernel stays the default;
   // NVN_WIDE_ROWS=twophase switches for experiments.
+  // Rows that need a cluster but do not fill its shape lose the ring (equal slices) and run
+  // with idle lanes; measured on B200 (bf16 widths 20000 ... 200000, fp32 20000 / 50000) the
+  // two-phase kernels are 10-40 % faster there, so they take those.
+  const char* wide_env = getenv("NVN_WIDE_ROWS");
+  const bool want_colslice = wide_env != nullptr && wide_env[0] == 'c' && wide_env[1] == 'o';
+  if (!p->two_phase && full && table[table_index].cs > 1 && cap(table[table_index]) != nvec &&
+      rows <= 0x7fffffffLL && !want_colslice)
+    p->two_phase = true;
   if (!p->two_phase && table[table_index].cs > 1) {
     const char* v = getenv("NVN_WIDE_ROWS");
     if (v != nullptr && v[0] == 't') p->two_phase = true;
