@@ -182,6 +182,13 @@ int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int
   if (!p->two_phase && full && table[table_index].cs > 1 && cap(table[table_index]) != nvec &&
       rows <= 0x7fffffffLL && !want_colslice)
     p->two_phase = true;
+  // Forward over cluster shapes pays two cluster barriers per row; once the problem is large
+  // (>= 64 MB per tensor) the three-pass two-phase kernels are faster (fp16 [1024, 65536]:
+  // 3.6 against 2.6 TB/s), while few rows ([256, 65536]: 25 against 29 us) stay on clusters.
+  if (!p->two_phase && !bwd && full && table[table_index].cs > 1 && rows <= 0x7fffffffLL &&
+      !want_colslice && rows * D * static_cast<int64_t>(dtype_size(dtype)) >= kHeldRingMinBytes &&
+      !(wide_env != nullptr && wide_env[0] == 'c'))
+    p->two_phase = true;
   if (!p->two_phase && table[table_index].cs > 1) {
     const char* v = getenv("NVN_WIDE_ROWS");
     if (v != nullptr && v[0] == 't') p->two_phase = true;
