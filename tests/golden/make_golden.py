@@ -8,9 +8,9 @@ its fused gradient ops.  The test modules import TensorFlow at the top, which is
 not installed, so the two function definitions are pulled out of the source with
 ``ast`` and executed with NumPy alone; nothing is copied into this repository.
 
-Run from the repository root in the container that has the reference mounted:
+Run from the repository root, giving the path of a checkout of the reference:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path-to-atex-checkout>
 
 Shapes are taken from the reference's test matrix (typical, odd, rank-3/4 inputs,
 both InstanceNorm layouts).  The saved statistics fed to the gradient functions are
@@ -115,4 +115,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <path-to-atex-checkout>")
+    main(sys.argv[1])
