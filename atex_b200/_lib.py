@@ -9,8 +9,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# NVN_LIB_PATH points experiments at an alternative build of the same library.
-LIB_PATH = os.environ.get("NVN_LIB_PATH") or os.path.join(_HERE, "libnvnorms.so")
+LIB_PATH = os.path.join(_HERE, "libnvnorms.so")
 
 NVN_F32, NVN_F16, NVN_BF16 = 0, 1, 2
 
@@ -68,6 +67,7 @@ SIGNATURES = {
     "nvn_dp_recv_bytes": (_sz, [_i64, _int]),
     "nvn_ln_bwd_dp": (_int, [_int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _sz,
                              _c.POINTER(DpComm), _vp]),
+    "nvn_ln_bwd_noalloc": (_int, [_int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp]),
     "nvn_in_bwd_dp": (_int, [_int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _vp, _vp,
                              _vp, _sz, _c.POINTER(DpComm), _vp]),
 }

@@ -22,7 +22,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OBJDIR = os.path.join(CSRC, "build")
-LIB = os.environ.get("NVN_LIB_OUT") or os.path.join(HERE, "libnvnorms.so")
+LIB = os.path.join(HERE, "libnvnorms.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -30,9 +30,6 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-fvisibility=hidden",
     "-I", INCLUDE,
 ]
-# Extra compiler flags for experiments (for example a pre-included header that
-# overrides the shape tables); empty in normal builds.
-NVCC_FLAGS += os.environ.get("NVN_EXTRA_NVCC_FLAGS", "").split()
 
 
 def _units():
@@ -43,13 +40,10 @@ def _units():
     units.append(("twophase.o", "twophase.cu", []))
     units.append(("colreduce.o", "colreduce.cu", []))
     units.append(("colreduce_dp.o", "colreduce_dp.cu", []))
-    units.append(("colslice.o", "colslice.cu", []))
     units.append(("nlc_onchip.o", "nlc_onchip.cu", []))
     units.append(("nlc_small.o", "nlc_small.cu", []))
     units.append(("nvnorms_api.o", "nvnorms_api.cu", []))
-    extra = os.path.join(CSRC, "noalloc.cu")
-    if os.path.exists(extra):
-        units.append(("noalloc.o", "noalloc.cu", []))
+    units.append(("noalloc.o", "noalloc.cu", []))
     return units
 
 

@@ -18,9 +18,12 @@
 // bit-identical on all ranks and from run to run.  Each CTA pushes before it polls and
 // only waits for CTAs of other GPUs, so no CTA waits for one that cannot be scheduled.
 // Four receive slots (epoch mod 4): with a single fused launch a rank can only get one
-// epoch ahead of the slowest rank (finishing epoch e needs every rank's push of e); in
+// epoch ahead of the slowest rank (finishing epoch e needs every rank's push of e).  In
 // the deferred form (push now, finish later on another stream) the caller keeps the push
-// of epoch e+1 behind its own finish of epoch e-2, which keeps every slot's readers done
+// of epoch e behind its own finish of epoch e-2.  That is enough across ranks: rank A's
+// finish of e-2 needed rank B's push of e-2, which B issued after its own finish of e-4,
+// the last reader of the slot that A's push of e overwrites at B.  (Lagging the finish by
+// L epochs needs 2L slots; the four slots here give L = 2.)  Every slot's readers are done
 // before it is overwritten.  A poll that exceeds its limit raises the device status word
 // and the kernel finishes with whatever arrived; it never hangs.  No multimem and no
 // multicast instruction is used: plain st / ld.
@@ -104,6 +107,7 @@ __global__ void __launch_bounds__(kTX* TY)
   if constexpr (!FINISH) return;
   // bounded poll of this rank's own receive rows, then the sum in rank order
   int ok = 1;
+  unsigned polls = 0;
   float acc[kW] = {0.f, 0.f, 0.f, 0.f};
   if (ty == 0 && col < F2) {
     for (int r = 0; r < c.world; ++r) {
@@ -111,12 +115,10 @@ __global__ void __launch_bounds__(kTX* TY)
 #pragma unroll
       for (int w = 0; w < kW; ++w) {
         uint2 v = ld_pair(src + w);
-        unsigned polls = 0;
-        while (v.y != c.epoch) {
-          if (++polls > kPollLimit) {
-            ok = 0;
-            break;
-          }
+        // one budget for the whole thread: after the first element that never arrives the
+        // rest are read once and not waited for, so a missing peer costs one time-out
+        while (v.y != c.epoch && ok) {
+          if (++polls > kPollLimit) ok = 0;
           v = ld_pair(src + w);
         }
         acc[w] += __uint_as_float(v.x);

@@ -286,15 +286,17 @@ template <typename T, bool BWD, int STAGES>
 cudaError_t launch_s(NlcOnchipArgs& a, size_t slab_bytes, cudaStream_t s) {
   auto kernel = nlc_onchip_kernel<T, BWD, STAGES>;
   const size_t smem = slab_bytes * STAGES;
-  // Per process and kernel: the opt-in to large dynamic shared memory, and the occupancy for
-  // the last slab size seen (every device this library runs on is the same part).
-  static std::atomic<int> prepared{0};
+  // The opt-in to large dynamic shared memory is set once per device; the occupancy for the
+  // last slab size seen is cached per process (every device this library runs on is the
+  // same part).
+  static std::atomic<uint64_t> prepared{0};
   static std::atomic<int64_t> cached{0};  // (smem << 8) | CTAs per SM
-  if (prepared.load(std::memory_order_acquire) == 0) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(kSlabMax));
+  {
+    const cudaError_t e = once_per_device(prepared, [&]() -> cudaError_t {
+      return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(kSlabMax));
+    });
     if (e != cudaSuccess) return e;
-    prepared.store(1, std::memory_order_release);
   }
   int per_sm = 0;
   const int64_t c = cached.load(std::memory_order_relaxed);

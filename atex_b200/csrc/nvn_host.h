@@ -45,20 +45,6 @@ struct RowsPlan {
   int partial_rows;  // rows of [2][D] dgamma/dbeta partials the backward kernel writes
 };
 
-// Column-sliced LayerNorm kernels for wide rows (colslice.cu): every CTA owns 4 * vpl
-// vectors of every row; per-row partial sums meet behind a grid barrier.
-struct ColslicePlan {
-  int vpl;               // lanes that share a row slice (4 vectors per lane)
-  int grid;              // CTAs = column slices
-  size_t partial_bytes;  // [rows][grid] float2
-};
-bool colslice_plan(int64_t nvec, int64_t rows, ColslicePlan* p);
-// Backward writes the final dgamma / dbeta.  `partials` holds plan.partial_bytes, `counter`
-// one 32-bit word (zeroed by the launch itself).
-cudaError_t colslice_launch(int dtype, bool bwd, const ColslicePlan& p, const RowsArgs& r,
-                            float* dgamma, float* dbeta, void* partials, void* counter,
-                            cudaStream_t s);
-
 // On-chip channels-last InstanceNorm (nlc_onchip.cu): one CTA holds a whole batch item in
 // shared memory.  nlc_onchip_ok: the item fits and C / vector divides the CTA size.  The
 // backward launch leaves per-item (dgamma, dbeta) contributions in colpart[N][2][C].
@@ -96,6 +82,26 @@ inline cudaLaunchConfig_t dependent_launch_config(dim3 grid, dim3 block, size_t 
 
 int device_sm_count();
 void count_launch();
+
+// Function attributes (the opt-in to more than 48 KB of dynamic shared memory, non-portable
+// cluster sizes) belong to one device's context, and one process may drive several devices
+// (a TensorFlow process owns every GPU of the node).  `mask` is a kernel's own set of device
+// ordinals whose context already has the attributes; `set` runs with the calling thread's
+// current device when that device is not in the set yet.  Two threads may both run `set`
+// the first time: the calls are idempotent.
+template <typename F>
+inline cudaError_t once_per_device(std::atomic<uint64_t>& mask, F&& set) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  // ordinals beyond 63 are not remembered: every call sets the attributes again
+  const uint64_t bit = (dev >= 0 && dev < 64) ? (1ull << dev) : 0;
+  if (bit != 0 && (mask.load(std::memory_order_acquire) & bit) != 0) return cudaSuccess;
+  e = set();
+  if (e != cudaSuccess) return e;
+  if (bit != 0) mask.fetch_or(bit, std::memory_order_release);
+  return cudaSuccess;
+}
 // Device address of the library's status word on the current device (nullptr on failure).
 int* device_status_word();
 

@@ -15,6 +15,8 @@
 #include <algorithm>
 #include <atomic>
 #include <mutex>
+#include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/nvnorms.h"
@@ -49,19 +51,51 @@ inline int64_t cap(const Shape& s) { return static_cast<int64_t>(s.tpr) * s.vpt 
 // [65536, 2048] bf16, 268 MB, where the held ring is 15 % faster).
 constexpr int64_t kHeldRingMinBytes = 64ll << 20;
 
-// Smallest capacity that holds `nvec` vectors; among equals the first listed, skipping
-// held-ring entries for problems of less than kHeldRingMinBytes per tensor.
-// NVN_FORCE_FWD_SHAPE / NVN_FORCE_BWD_SHAPE (a table index) override the
-// choice when that shape is large enough: used for tuning runs only.
-int pick_shape(const Shape* table, int n, int64_t nvec, int64_t tensor_bytes,
-               const char* force_env) {
-  if (force_env != nullptr) {
-    const char* v = getenv(force_env);
-    if (v != nullptr && *v != '\0') {
-      const int idx = atoi(v);
-      if (idx >= 0 && idx < n && cap(table[idx]) >= nvec) return idx;
+// The one experiment switch of the library, off by default: the environment variable
+// NVN_FORCE_VARIANT, read once when the library is first used, holds comma-separated
+// key=value pairs that override the dispatcher for profiler and tuning runs:
+//   wide=twophase|cluster   path of contiguous rows that need a thread-block cluster
+//   nlc=twophase|onchip     channels-last InstanceNorm: skip the on-chip and / or the
+//                           warp-per-item kernels
+//   fwd_shape=I bwd_shape=I affine_shape=I   index into the shape tables of nvn_host.h
+//                           (used when that shape is large enough for the row)
+struct Variant {
+  int wide = 0;  // 0 default, 1 two-phase, 2 cluster
+  int nlc = 0;   // 0 default, 1 two-phase, 2 on-chip but no warp-per-item
+  int fwd_shape = -1, bwd_shape = -1, affine_shape = -1;
+};
+
+const Variant& variant() {
+  static const Variant v = [] {
+    Variant r;
+    const char* env = getenv("NVN_FORCE_VARIANT");
+    if (env == nullptr) return r;
+    std::string text(env);
+    size_t pos = 0;
+    while (pos < text.size()) {
+      size_t end = text.find(',', pos);
+      if (end == std::string::npos) end = text.size();
+      const std::string item = text.substr(pos, end - pos);
+      pos = end + 1;
+      const size_t eq = item.find('=');
+      if (eq == std::string::npos) continue;
+      const std::string key = item.substr(0, eq), val = item.substr(eq + 1);
+      if (key == "wide") r.wide = val == "twophase" ? 1 : (val == "cluster" ? 2 : 0);
+      if (key == "nlc") r.nlc = val == "twophase" ? 1 : (val == "onchip" ? 2 : 0);
+      if (key == "fwd_shape") r.fwd_shape = atoi(val.c_str());
+      if (key == "bwd_shape") r.bwd_shape = atoi(val.c_str());
+      if (key == "affine_shape") r.affine_shape = atoi(val.c_str());
     }
-  }
+    return r;
+  }();
+  return v;
+}
+
+// Smallest capacity that holds `nvec` vectors; among equals the first listed, skipping
+// held-ring entries for problems of less than kHeldRingMinBytes per tensor.  `forced` (a
+// table index from NVN_FORCE_VARIANT, or -1) wins when that shape is large enough.
+int pick_shape(const Shape* table, int n, int64_t nvec, int64_t tensor_bytes, int forced) {
+  if (forced >= 0 && forced < n && cap(table[forced]) >= nvec) return forced;
   int best = -1;
   for (int pass = 0; pass < 2 && best < 0; ++pass) {
     for (int i = 0; i < n; ++i) {
@@ -134,9 +168,6 @@ struct RowProblemPlan {
   bool two_phase;
   size_t off_colscratch;  // slab scratch of the column reduction (0 bytes: none)
   bool has_colscratch;
-  bool colslice;   // wide LayerNorm rows: column-sliced kernels behind a grid barrier
-  ColslicePlan cs;
-  size_t off_cs_part, off_cs_counter;
   bool scalar;     // two-phase variant runs element-wise
   int epv;         // elements per access of the row-cached variant
   int shape;       // row-cached variant
@@ -148,9 +179,10 @@ struct RowProblemPlan {
 };
 
 // align: alignment shared by every pointer (16 is assumed for size queries).
-int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int64_t N,
-              int64_t C, size_t align, size_t par_align, RowProblemPlan* p) {
+int plan_rows_uncached(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int64_t N,
+                       int64_t C, size_t align, size_t par_align, RowProblemPlan* p) {
   memset(p, 0, sizeof(*p));
+  const Variant& var = variant();
   const int V = full_epv(dtype);
   int epv = pick_epv(dtype, D, align, par_align);
   p->epv = epv;
@@ -163,59 +195,27 @@ int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int
                              : (heavy ? kHeavyShapes : (affine_wide ? kAffineWideShapes : kLightShapes));
   const int ntab =
       !full ? kNumScalar : (heavy ? kNumHeavy : (affine_wide ? kNumAffineWide : kNumLight));
-  const char* env = !full ? nullptr
-                          : (affine_wide ? "NVN_FORCE_AFFINE_SHAPE"
-                                         : (bwd ? "NVN_FORCE_BWD_SHAPE" : "NVN_FORCE_FWD_SHAPE"));
-  p->shape = pick_shape(table, ntab, nvec, rows * D * static_cast<int64_t>(dtype_size(dtype)), env);
+  const int forced = !full ? -1
+                           : (affine_wide ? var.affine_shape : (bwd ? var.bwd_shape : var.fwd_shape));
+  const int64_t tensor_bytes = rows * D * static_cast<int64_t>(dtype_size(dtype));
+  p->shape = pick_shape(table, ntab, nvec, tensor_bytes, forced);
   p->two_phase = p->shape < 0;
   const int table_index = p->shape;  // `table[table_index]` below; p->shape is what the launcher gets
   if (affine_wide && p->shape >= 0) p->shape += kAffineWideBase;
-  // Rows that need a cluster could also take the two-phase path (phase 2 then re-reads
-  // from L2 when the problem is small).  Measured on B200 for [256, 65536] fp16 the two are
-  // equal (70 us fwd+bwd), so the single-launch cluster kernel stays the default;
-  // NVN_WIDE_ROWS=twophase switches for experiments.
+  const bool clustered = !p->two_phase && table[table_index].cs > 1;
   // Rows that need a cluster but do not fill its shape lose the ring (equal slices) and run
   // with idle lanes; measured on B200 (bf16 widths 20000 ... 200000, fp32 20000 / 50000) the
   // two-phase kernels are 10-40 % faster there, so they take those.
-  const char* wide_env = getenv("NVN_WIDE_ROWS");
-  const bool want_colslice = wide_env != nullptr && wide_env[0] == 'c' && wide_env[1] == 'o';
-  if (!p->two_phase && full && table[table_index].cs > 1 && cap(table[table_index]) != nvec &&
-      rows <= 0x7fffffffLL && !want_colslice)
+  if (clustered && full && cap(table[table_index]) != nvec && rows <= 0x7fffffffLL && var.wide != 2)
     p->two_phase = true;
   // Forward over cluster shapes pays two cluster barriers per row; once the problem is large
   // (>= 64 MB per tensor) the three-pass two-phase kernels are faster (fp16 [1024, 65536]:
   // 3.6 against 2.6 TB/s), while few rows ([256, 65536]: 25 against 29 us) stay on clusters.
-  if (!p->two_phase && !bwd && full && table[table_index].cs > 1 && rows <= 0x7fffffffLL &&
-      !want_colslice && rows * D * static_cast<int64_t>(dtype_size(dtype)) >= kHeldRingMinBytes &&
-      !(wide_env != nullptr && wide_env[0] == 'c'))
+  if (clustered && !bwd && full && rows <= 0x7fffffffLL && tensor_bytes >= kHeldRingMinBytes &&
+      var.wide != 2)
     p->two_phase = true;
-  if (!p->two_phase && table[table_index].cs > 1) {
-    const char* v = getenv("NVN_WIDE_ROWS");
-    if (v != nullptr && v[0] == 't') p->two_phase = true;
-  }
+  if (clustered && var.wide == 1) p->two_phase = true;
   size_t off = 0;
-  // Experimental: LayerNorm rows of more than 2048 vectors cut by columns instead of rows
-  // (colslice.cu).  Correct, but on B200 still slower than the cluster shapes
-  // ([256, 65536] fp16: 35 + 49 us against 25 + 36 us), so it only runs on request
-  // (NVN_WIDE_ROWS=colslice).
-  if (!row_affine && full && nvec > 2048 && !p->two_phase) {
-    const char* v = getenv("NVN_WIDE_ROWS");
-    if (v != nullptr && v[0] == 'c' && v[1] == 'o' && colslice_plan(nvec, rows, &p->cs)) {
-      p->colslice = true;
-      p->off_cs_part = off;
-      off += align_up(p->cs.partial_bytes, 256);
-      p->off_cs_counter = off;
-      off += 256;
-      if (bwd) {
-        // one row of [dgamma | dbeta] for the data-parallel exchange to pick up
-        p->colpart_rows = 1;
-        p->off_colpart = off;
-        off += align_up(static_cast<size_t>(2) * D * 4, 256);
-      }
-      p->bytes = off;
-      return NVN_OK;
-    }
-  }
   if (!p->two_phase) {
     RowsArgs a = {};
     a.N = rows;
@@ -254,16 +254,72 @@ int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int
   return NVN_OK;
 }
 
+// Plans are pure functions of the problem (every device this library runs on is the same
+// part), and a training step asks for the same few over and over: once for the workspace
+// size and once per launch.  A small table keyed by the problem keeps the dispatcher out of
+// the per-call cost.
+struct PlanKey {
+  int64_t rows, D, N, C;
+  int dtype, flags, align, par_align;
+  bool operator==(const PlanKey& o) const {
+    return rows == o.rows && D == o.D && N == o.N && C == o.C && dtype == o.dtype &&
+           flags == o.flags && align == o.align && par_align == o.par_align;
+  }
+};
+struct PlanKeyHash {
+  size_t operator()(const PlanKey& k) const {
+    uint64_t h = 0x9e3779b97f4a7c15ull;
+    for (uint64_t v : {static_cast<uint64_t>(k.rows), static_cast<uint64_t>(k.D),
+                       static_cast<uint64_t>(k.N), static_cast<uint64_t>(k.C),
+                       static_cast<uint64_t>(k.dtype * 64 + k.flags),
+                       static_cast<uint64_t>(k.align * 32 + k.par_align)})
+      h = (h ^ v) * 0xff51afd7ed558ccdull + (h >> 29);
+    return static_cast<size_t>(h);
+  }
+};
+template <typename Plan>
+struct PlanCache {
+  std::mutex mu;
+  std::unordered_map<PlanKey, Plan, PlanKeyHash> map;
+  bool find(const PlanKey& k, Plan* out) {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = map.find(k);
+    if (it == map.end()) return false;
+    *out = it->second;
+    return true;
+  }
+  void put(const PlanKey& k, const Plan& p) {
+    std::lock_guard<std::mutex> lock(mu);
+    if (map.size() >= 1024) map.clear();  // a bound, not a policy: real jobs use a handful
+    map[k] = p;
+  }
+};
+PlanCache<RowProblemPlan> g_row_plans;
+PlanCache<size_t> g_ws_bytes;
+
+int plan_rows(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D, int64_t N,
+              int64_t C, size_t align, size_t par_align, RowProblemPlan* p) {
+  const PlanKey key = {rows, D, N, C, dtype, (bwd ? 1 : 0) | (row_affine ? 2 : 0),
+                       static_cast<int>(align), static_cast<int>(par_align)};
+  if (g_row_plans.find(key, p)) return NVN_OK;
+  const int st = plan_rows_uncached(dtype, bwd, row_affine, rows, D, N, C, align, par_align, p);
+  if (st == NVN_OK) g_row_plans.put(key, *p);
+  return st;
+}
+
 size_t rows_workspace_bytes(int dtype, bool bwd, bool row_affine, int64_t rows, int64_t D,
                             int64_t N, int64_t C) {
   if (rows <= 0 || D <= 0) return 0;
-  RowProblemPlan pv;
+  const PlanKey key = {rows, D, N, C, dtype, (bwd ? 1 : 0) | (row_affine ? 2 : 0) | 4, 0, 0};
   size_t b = 0;
+  if (g_ws_bytes.find(key, &b)) return b;
+  RowProblemPlan pv;
   // the workspace can depend on the access width, which depends on the caller's alignment
   for (size_t al : {size_t(16), size_t(8), size_t(4), size_t(2)}) {
     if (plan_rows(dtype, bwd, row_affine, rows, D, N, C, al, 16, &pv) == NVN_OK)
       b = std::max(b, pv.bytes);
   }
+  g_ws_bytes.put(key, b);
   return b;
 }
 
@@ -282,35 +338,6 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
   char* wsb = static_cast<char*>(ws);
   const int64_t F = row_affine ? C : D;
 
-  if (p.colslice) {
-    RowsArgs a = {};
-    a.x = x;
-    a.dy = dy;
-    a.gamma = gamma;
-    a.beta = beta;
-    a.mean_in = mean_in;
-    a.ivar_in = ivar_in;
-    a.out = out;
-    a.mean = mean;
-    a.ivar = ivar;
-    a.N = rows;
-    a.D = D;
-    a.C = C;
-    a.eps = eps;
-    a.status = device_status_word();
-    // alone, the kernel writes dgamma / dbeta itself; with a data-parallel exchange they go
-    // to the workspace as the single partial row the exchange kernel sums and sends
-    float* colpart = bwd ? reinterpret_cast<float*>(wsb + p.off_colpart) : nullptr;
-    cudaError_t e = colslice_launch(dtype, bwd, p.cs, a, comm != nullptr ? colpart : dgamma,
-                                    comm != nullptr ? colpart + D : dbeta, wsb + p.off_cs_part,
-                                    wsb + p.off_cs_counter, stream);
-    if (e != cudaSuccess) return fail_cuda(e);
-    if (bwd && comm != nullptr) {
-      e = colreduce_allreduce_launch(colpart, 1, F, comm, dgamma, dbeta, stream);
-      if (e != cudaSuccess) return fail_cuda(e);
-    }
-    return NVN_OK;
-  }
   if (!p.two_phase) {
     RowsArgs a = {};
     a.x = x;
@@ -388,8 +415,7 @@ int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, 
   // one-launch path for channel counts or alignments the vector kernels cannot take.
   const bool onchip_ok = vec_ok && allow_onchip && nlc_onchip_ok(dtype, bwd, C, D);
   if (nlc_small_ok(C, D) && (D * C <= 2048 || !onchip_ok)) {
-    const char* v = getenv("NVN_NLC");
-    if (!(v != nullptr && (v[0] == 't' || v[0] == 'o'))) {
+    if (variant().nlc == 0) {
       p->small = true;
       p->off_colpart = 0;
       p->bytes = bwd ? align_up(static_cast<size_t>(N) * 2 * C * 4, 256) : 0;
@@ -403,8 +429,7 @@ int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, 
     }
   }
   if (onchip_ok) {
-    const char* v = getenv("NVN_NLC");  // NVN_NLC=twophase keeps the two-phase kernels
-    if (!(v != nullptr && v[0] == 't')) {
+    if (variant().nlc != 1) {
       p->onchip = true;
       p->off_colpart = 0;
       p->bytes = bwd ? align_up(static_cast<size_t>(N) * 2 * C * 4, 256) : 0;
@@ -850,10 +875,7 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
   RowProblemPlan p;
   int st = plan_rows(dtype, bwd, is_in, rows, D, N, is_in ? C : 1, 16, 16, &p);
   if (st != NVN_OK) return st;
-  if (p.colslice) {
-    snprintf(out, out_bytes, "colslice lanes=%d vpl=4 epv=%d grid=%d", p.cs.vpl, p.epv,
-             p.cs.grid);
-  } else if (p.two_phase) {
+  if (p.two_phase) {
     snprintf(out, out_bytes, "rows two-phase epv=%d chunk=%lld nchunks=%d slices=%d",
              p.scalar ? 1 : full_epv(dtype), static_cast<long long>(p.r2.chunk), p.r2.nchunks,
              p.r2.slices);

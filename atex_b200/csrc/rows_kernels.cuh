@@ -844,28 +844,30 @@ inline cudaError_t launch_rows_exact(const RowsArgs& a, cudaStream_t stream, boo
     kernel = rows_fwd_kernel<T, EPV, TPR, VPT, CS, RB, PR, MINB, PF, (EXACT || (TMA && CS > 1)),
                              ROW_AFFINE>;
   }
-  // Cached per process: every device this library runs on is the same part.  The
-  // occupancy depends on the ring size, which depends on D.
+  // The attributes are set once per device; the occupancy is cached per process (every
+  // device this library runs on is the same part) and depends on the ring size, hence on D.
   static std::atomic<int64_t> cached{0};  // (ring bytes << 20) | units
-  static std::atomic<int> prepared{0};
-  if (prepared.load(std::memory_order_acquire) == 0) {
-    if (CS > 8) {
-      cudaError_t e =
-          cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-      if (e != cudaSuccess) return e;
-    }
-    if (TMA) {
-      // the ring shares the SM's 227 KB with the kernel's static shared memory
-      cudaFuncAttributes fa;
-      cudaError_t e = cudaFuncGetAttributes(&fa, kernel);
-      if (e != cudaSuccess) return e;
-      const size_t room = 227 * 1024 - fa.sharedSizeBytes - 1024;
-      const size_t most = PF >= 10 ? kMaxHeldRingBytes : kMaxRingBytes;
-      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               static_cast<int>(most < room ? most : room));
-      if (e != cudaSuccess) return e;
-    }
-    prepared.store(1, std::memory_order_release);
+  static std::atomic<uint64_t> prepared{0};
+  {
+    const cudaError_t e = once_per_device(prepared, [&]() -> cudaError_t {
+      if (CS > 8) {
+        cudaError_t e1 =
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e1 != cudaSuccess) return e1;
+      }
+      if (TMA) {
+        // the ring shares the SM's 227 KB with the kernel's static shared memory
+        cudaFuncAttributes fa;
+        cudaError_t e1 = cudaFuncGetAttributes(&fa, kernel);
+        if (e1 != cudaSuccess) return e1;
+        const size_t room = 227 * 1024 - fa.sharedSizeBytes - 1024;
+        const size_t most = PF >= 10 ? kMaxHeldRingBytes : kMaxRingBytes;
+        return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(most < room ? most : room));
+      }
+      return cudaSuccess;
+    });
+    if (e != cudaSuccess) return e;
   }
   int units = 0;
   const int64_t c = cached.load(std::memory_order_relaxed);

@@ -20,6 +20,7 @@ accepts bfloat16.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from typing import Iterable, List, Sequence, Tuple
 
@@ -50,15 +51,45 @@ _DTYPE_CODE = {torch.float32: _lib.NVN_F32, torch.float16: _lib.NVN_F16,
 _workspaces = {}
 
 
-def _workspace(device: torch.device, nbytes: int) -> Tuple[int, int]:
+def _workspace(device: torch.device, stream: int, nbytes: int) -> Tuple[int, int]:
     if nbytes == 0:
         return 0, 0
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index, stream)
     ws = _workspaces.get(key)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+    if ws is None or ws[1] < nbytes:
+        t = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        ws = (t.data_ptr(), t.numel(), t)
         _workspaces[key] = ws
-    return ws.data_ptr(), ws.numel()
+    return ws[0], ws[1]
+
+
+# Shape bookkeeping and workspace sizes are pure functions of the problem; a training loop
+# asks for the same few on every step, so they are remembered (bounded, see _remember).
+_dims_cache = {}
+_ws_bytes_cache = {}
+
+
+def _remember(cache: dict, key, value):
+    if len(cache) >= 4096:
+        cache.clear()
+    cache[key] = value
+    return value
+
+
+def _ws_bytes(fn_name: str, *args) -> int:
+    key = (fn_name,) + args
+    v = _ws_bytes_cache.get(key)
+    if v is None:
+        v = _remember(_ws_bytes_cache, key, int(getattr(_lib.load(), fn_name)(*args)))
+    return v
+
+
+def _device_guard(device: torch.device):
+    """Makes `device` current for the C-ABI call (it works on the calling thread's current
+    device); free when it already is."""
+    if torch.cuda.current_device() == device.index:
+        return contextlib.nullcontext()
+    return torch.cuda.device(device)
 
 
 def _require(cond: bool, *msg) -> None:
@@ -114,6 +145,10 @@ def _shape_str(t: torch.Tensor) -> str:
 
 def _ln_dims(x: torch.Tensor, axis: Sequence[int]) -> Tuple[int, int]:
     """GetBatchAndFeatureSizes (fused_layer_norm_op.cc:252-282) through the C ABI."""
+    key = (tuple(x.shape), tuple(axis))
+    hit = _dims_cache.get(key)
+    if hit is not None:
+        return hit
     rank = x.dim()
     dims = (ctypes.c_int64 * max(rank, 1))(*[int(s) for s in x.shape])
     ax = (ctypes.c_int * max(len(axis), 1))(*[int(a) for a in axis])
@@ -123,10 +158,14 @@ def _ln_dims(x: torch.Tensor, axis: Sequence[int]) -> Tuple[int, int]:
         bad = [a for a in axis if not (0 <= (a + rank if a < 0 else a) < rank)]
         raise InvalidArgumentError(f"axis contains invalid value: {bad[0] if bad else axis}")
     _check(st, "nvn_ln_dims")
-    return N.value, D.value
+    return _remember(_dims_cache, key, (N.value, D.value))
 
 
 def _in_dims(x: torch.Tensor, data_format: str) -> Tuple[int, int, int, bool]:
+    key = (tuple(x.shape), str(data_format))
+    hit = _dims_cache.get(key)
+    if hit is not None:
+        return hit
     rank = x.dim()
     dims = (ctypes.c_int64 * max(rank, 1))(*[int(s) for s in x.shape])
     N, C, D, cf = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int()
@@ -138,7 +177,7 @@ def _in_dims(x: torch.Tensor, data_format: str) -> Tuple[int, int, int, bool]:
     if st == _lib.NVN_ERR_RANK:
         raise InvalidArgumentError(f"input must be at least 4-dimensional{_shape_str(x)}")
     _check(st, "nvn_in_dims")
-    return N.value, C.value, D.value, bool(cf.value)
+    return _remember(_dims_cache, key, (N.value, C.value, D.value, bool(cf.value)))
 
 
 def _axis_list(axis) -> List[int]:
@@ -154,14 +193,40 @@ def _stream(device: torch.device) -> int:
 # ---------------------------------------------------------------------------
 # raw ops
 # ---------------------------------------------------------------------------
+def _stats_outputs(shape, device, out_stats):
+    """mean / inv_std buffers: fresh, or the caller's pair of contiguous float32 tensors."""
+    if out_stats is None:
+        return (torch.empty(shape, dtype=torch.float32, device=device),
+                torch.empty(shape, dtype=torch.float32, device=device))
+    mean, inv_std = out_stats
+    n = 1
+    for s_ in (shape if isinstance(shape, tuple) else (shape,)):
+        n *= s_
+    for t in (mean, inv_std):
+        if (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()
+                or t.device != device):
+            raise ValueError("out_stats must be two contiguous float32 tensors of the statistics' size")
+    return mean, inv_std
+
+
+def _like_output(x, out, name):
+    if out is None:
+        return torch.empty_like(x)
+    if out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous() or out.device != x.device:
+        raise ValueError(f"{name} must be a contiguous tensor like x")
+    return out
+
+
 def fused_layer_norm_op(x, scale, offset, axis: Iterable[int] = (-1,), epsilon: float = 0.001,
-                        out: torch.Tensor | None = None):
+                        out: torch.Tensor | None = None, out_stats=None):
     """FusedLayerNorm (norm_ops.cc:148-159): returns (y, reserve_space_1, reserve_space_2).
 
     reserve_space_1 is the per-row mean and reserve_space_2 the per-row
     1/sqrt(var + epsilon), both float32 of shape [N] with N the product of the
     non-normalised leading dims.  `out` may be `x` itself to normalise in place
-    (the reference forwards its input buffer the same way).
+    (the reference forwards its input buffer the same way); `out_stats` optionally supplies
+    the (reserve_space_1, reserve_space_2) buffers, so that a steady-state loop allocates
+    nothing.
     """
     _require(isinstance(x, torch.Tensor) and x.dim() > 0, "input must be at least 1-dimensional",
              x if isinstance(x, torch.Tensor) else "")
@@ -174,20 +239,15 @@ def fused_layer_norm_op(x, scale, offset, axis: Iterable[int] = (-1,), epsilon: 
     _require(offset.numel() == D, "offset must have the same number of elements as the features "
              "of x, got ", offset.numel(), " and ", D)
     x, scale, offset = _on_device((x, "x"), (scale, "scale"), (offset, "offset"))
-    if out is None:
-        y = torch.empty_like(x)
-    else:
-        if out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous() or out.device != x.device:
-            raise ValueError("out must be a contiguous tensor like x")
-        y = out
-    mean = torch.empty(N, dtype=torch.float32, device=x.device)
-    inv_std = torch.empty(N, dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    y = _like_output(x, out, "out")
+    mean, inv_std = _stats_outputs(N, x.device, out_stats)
+    with _device_guard(x.device):
         lib = _lib.load()
-        ws_ptr, ws_bytes = _workspace(x.device, lib.nvn_ln_fwd_workspace_bytes(code, N, D))
+        stream = _stream(x.device)
+        ws_ptr, ws_bytes = _workspace(x.device, stream, _ws_bytes("nvn_ln_fwd_workspace_bytes", code, N, D))
         st = lib.nvn_ln_fwd(code, x.data_ptr(), scale.data_ptr(), offset.data_ptr(), N, D,
                             float(epsilon), y.data_ptr(), mean.data_ptr(), inv_std.data_ptr(),
-                            ws_ptr, ws_bytes, _stream(x.device))
+                            ws_ptr, ws_bytes, stream)
     _check(st, "nvn_ln_fwd")
     return y, mean, inv_std
 
@@ -207,10 +267,11 @@ def _grad_outputs(scale: torch.Tensor, out_grads):
 
 def fused_layer_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_space_2,
                              axis: Iterable[int] = (-1,), epsilon: float = 0.001, out_grads=None,
-                             grad_exchange=None):
+                             grad_exchange=None, out: torch.Tensor | None = None):
     """FusedLayerNormGrad (norm_ops.cc:161-174): returns (x_backprop, scale_backprop,
     offset_backprop); the parameter gradients take the shape of `scale`.  `out_grads`
-    optionally supplies the (scale_backprop, offset_backprop) buffers.  With
+    optionally supplies the (scale_backprop, offset_backprop) buffers and `out` the
+    x_backprop buffer.  With
     `grad_exchange` (a sharding.GradExchange) the parameter gradients come back already
     summed over all data-parallel ranks."""
     _require(isinstance(y_backprop, torch.Tensor) and y_backprop.dim() > 0,
@@ -236,27 +297,27 @@ def fused_layer_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_spac
              "channels of x, got ", inv_std.numel(), " and ", N)
     x, dy, scale, mean, inv_std = _on_device((x, "x"), (dy, "y_backprop"), (scale, "scale"),
                                              (mean, "reserve_space_1"), (inv_std, "reserve_space_2"))
-    dx = torch.empty_like(x)
+    dx = _like_output(x, out, "out")
     dgamma, dbeta = _grad_outputs(scale, out_grads)
-    with torch.cuda.device(x.device):
+    with _device_guard(x.device):
         lib = _lib.load()
-        ws_ptr, ws_bytes = _workspace(x.device, lib.nvn_ln_bwd_workspace_bytes(code, N, D))
+        stream = _stream(x.device)
+        ws_ptr, ws_bytes = _workspace(x.device, stream, _ws_bytes("nvn_ln_bwd_workspace_bytes", code, N, D))
         if grad_exchange is None:
             st = lib.nvn_ln_bwd(code, dy.data_ptr(), x.data_ptr(), scale.data_ptr(),
                                 mean.data_ptr(), inv_std.data_ptr(), N, D, dx.data_ptr(),
-                                dgamma.data_ptr(), dbeta.data_ptr(), ws_ptr, ws_bytes,
-                                _stream(x.device))
+                                dgamma.data_ptr(), dbeta.data_ptr(), ws_ptr, ws_bytes, stream)
         else:
             st = lib.nvn_ln_bwd_dp(code, dy.data_ptr(), x.data_ptr(), scale.data_ptr(),
                                    mean.data_ptr(), inv_std.data_ptr(), N, D, dx.data_ptr(),
                                    dgamma.data_ptr(), dbeta.data_ptr(), ws_ptr, ws_bytes,
-                                   grad_exchange.next_comm(), _stream(x.device))
+                                   grad_exchange.next_comm(D), stream)
     _check(st, "nvn_ln_bwd")
     return dx, dgamma, dbeta
 
 
 def fused_instance_norm_op(x, scale, offset, data_format: str = "N...C", epsilon: float = 0.001,
-                           out: torch.Tensor | None = None):
+                           out: torch.Tensor | None = None, out_stats=None):
     """FusedInstanceNorm (norm_ops.cc:176-187): returns (y, reserve_space_1, reserve_space_2)
     with the statistics of shape [N, C]."""
     _require(isinstance(x, torch.Tensor), "input must be a tensor")
@@ -270,27 +331,23 @@ def fused_instance_norm_op(x, scale, offset, data_format: str = "N...C", epsilon
     _require(offset.numel() == C, "offset must have the same number of elements as the channels "
              "of x, got ", offset.numel(), " and ", C)
     x, scale, offset = _on_device((x, "x"), (scale, "scale"), (offset, "offset"))
-    if out is None:
-        y = torch.empty_like(x)
-    else:
-        if out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous() or out.device != x.device:
-            raise ValueError("out must be a contiguous tensor like x")
-        y = out
-    mean = torch.empty((N, C), dtype=torch.float32, device=x.device)
-    inv_std = torch.empty((N, C), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    y = _like_output(x, out, "out")
+    mean, inv_std = _stats_outputs((N, C), x.device, out_stats)
+    with _device_guard(x.device):
         lib = _lib.load()
-        ws_ptr, ws_bytes = _workspace(x.device, lib.nvn_in_fwd_workspace_bytes(code, N, C, D, int(cf)))
+        stream = _stream(x.device)
+        ws_ptr, ws_bytes = _workspace(
+            x.device, stream, _ws_bytes("nvn_in_fwd_workspace_bytes", code, N, C, D, int(cf)))
         st = lib.nvn_in_fwd(code, x.data_ptr(), scale.data_ptr(), offset.data_ptr(), N, C, D, int(cf),
                             float(epsilon), y.data_ptr(), mean.data_ptr(), inv_std.data_ptr(),
-                            ws_ptr, ws_bytes, _stream(x.device))
+                            ws_ptr, ws_bytes, stream)
     _check(st, "nvn_in_fwd")
     return y, mean, inv_std
 
 
 def fused_instance_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_space_2,
                                 data_format: str = "N...C", epsilon: float = 0.001, out_grads=None,
-                                grad_exchange=None):
+                                grad_exchange=None, out: torch.Tensor | None = None):
     """FusedInstanceNormGrad (norm_ops.cc:189-202): returns (x_backprop, scale_backprop,
     offset_backprop).  `out_grads` optionally supplies the two parameter-gradient buffers."""
     _require(isinstance(y_backprop, torch.Tensor) and y_backprop.dim() > 3,
@@ -317,21 +374,23 @@ def fused_instance_norm_grad_op(y_backprop, x, scale, reserve_space_1, reserve_s
              "the batches * channels of x, got ", inv_std.numel(), " and ", N * C)
     x, dy, scale, mean, inv_std = _on_device((x, "x"), (dy, "y_backprop"), (scale, "scale"),
                                              (mean, "reserve_space_1"), (inv_std, "reserve_space_2"))
-    dx = torch.empty_like(x)
+    dx = _like_output(x, out, "out")
     dgamma, dbeta = _grad_outputs(scale, out_grads)
-    with torch.cuda.device(x.device):
+    with _device_guard(x.device):
         lib = _lib.load()
-        ws_ptr, ws_bytes = _workspace(x.device, lib.nvn_in_bwd_workspace_bytes(code, N, C, D, int(cf)))
+        stream = _stream(x.device)
+        ws_ptr, ws_bytes = _workspace(
+            x.device, stream, _ws_bytes("nvn_in_bwd_workspace_bytes", code, N, C, D, int(cf)))
         if grad_exchange is None:
             st = lib.nvn_in_bwd(code, dy.data_ptr(), x.data_ptr(), scale.data_ptr(),
                                 mean.data_ptr(), inv_std.data_ptr(), N, C, D, int(cf),
                                 dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), ws_ptr,
-                                ws_bytes, _stream(x.device))
+                                ws_bytes, stream)
         else:
             st = lib.nvn_in_bwd_dp(code, dy.data_ptr(), x.data_ptr(), scale.data_ptr(),
                                    mean.data_ptr(), inv_std.data_ptr(), N, C, D, int(cf),
                                    dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), ws_ptr,
-                                   ws_bytes, grad_exchange.next_comm(), _stream(x.device))
+                                   ws_bytes, grad_exchange.next_comm(C), stream)
     _check(st, "nvn_in_bwd")
     return dx, dgamma, dbeta
 

@@ -52,6 +52,24 @@ def allreduce_param_grads(dgamma: torch.Tensor, dbeta: torch.Tensor, group=None,
     return buffer[:F].view(dgamma.shape), buffer[F:].view(dbeta.shape)
 
 
+NUM_SLOTS = 4   # receive slots of the fused exchange (epoch mod NUM_SLOTS)
+MAX_FINISH_LAG = NUM_SLOTS // 2   # a push of epoch e needs this rank's finish of e - MAX_FINISH_LAG
+
+
+def slot_of_epoch(epoch: int) -> int:
+    """Receive slot that the pushes of `epoch` write (epochs count from 1)."""
+    return epoch % NUM_SLOTS
+
+
+def push_allowed(epoch: int, finished_epoch: int) -> bool:
+    """May this rank push `epoch`, given that its own finishes up to `finished_epoch` are
+    complete?  The slot that the push overwrites at a peer was last read by that peer's
+    finish of epoch - NUM_SLOTS, which is complete once this rank's finish of
+    epoch - MAX_FINISH_LAG is (that finish needed the peer's push of the same epoch, which
+    the peer issued after its own finish of epoch - 2 * MAX_FINISH_LAG)."""
+    return finished_epoch >= epoch - MAX_FINISH_LAG
+
+
 class GradExchange:
     """Peer-memory buffers for the fused column-reduce + all-reduce of [dgamma | dbeta].
 
@@ -69,8 +87,9 @@ class GradExchange:
     def __init__(self, features: int, device: torch.device, group=None, deferred: bool = False):
         """deferred=True: the backward op only pushes this rank's vector; call finish()
         (typically on a side stream, see bench.py) to wait for the peers and obtain the sums.
-        Start the backward op of step e + 1 only after finish() of step e - 2 has completed
-        on this rank (the receive slots are reused every fourth step)."""
+        Start the backward op of step e only after finish() of step e - 2 has completed on
+        this rank: there are four receive slots (slot_of_epoch), and a finish that lags its
+        push by L steps needs 2L of them.  An instance is bound to one feature count."""
         lib = _lib.load()
         self.deferred = bool(deferred)
         self.features = int(features)
@@ -103,8 +122,13 @@ class GradExchange:
         for i in range(self.world):
             self._comm.recv[i] = recv_ptrs[i]
 
-    def next_comm(self):
-        """ctypes pointer to the nvn_dp_comm for the next call (advances the epoch)."""
+    def next_comm(self, features: int | None = None):
+        """ctypes pointer to the nvn_dp_comm for the next call (advances the epoch).
+        `features` is the caller's feature count: the receive buffers are laid out for the
+        count given at construction and cannot serve another."""
+        if features is not None and int(features) != self.features:
+            raise ValueError(f"this GradExchange was built for {self.features} features, "
+                             f"the op has {features}: use one exchange per feature count")
         self.epoch += 1
         self._comm.epoch = self.epoch
         return ctypes.byref(self._comm)

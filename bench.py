@@ -3,22 +3,30 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl ours|reference]
 
-One step = one forward + one backward pass of the workload's norm op over one batch
-(plus, on N > 1 GPUs, the single all-reduce of [dgamma | dbeta]).  The default workload
-is c2: LayerNorm, bf16 activations, [32768, 4096], fp32 gamma / beta.  Every rank owns
-one full batch of that shape (weak scaling, the data-parallel training arrangement), so
-`value` = N * algorithmic bytes / step time.
+One step = one forward + one backward pass of the workload's norm op over one batch (plus,
+on N > 1 GPUs, the single exchange of [dgamma | dbeta]).  The headline workload is c2:
+LayerNorm, bf16 activations, [32768, 4096], fp32 gamma / beta.
+
+Scaling.  On N > 1 GPUs the FIXED global batch is sharded over the ranks by default
+("scaling": "strong": c2's 32768 rows become 4096 rows per rank at N = 8); the same line
+carries the weak-scaling result (every rank a full batch) as the sub-record `weak`, the
+compute / exchange split of a step, and `dp_check`: the exchanged parameter gradients
+compared, outside the timed region, with one NCCL all-reduce of the local ones.
 
 Prints ONE JSON line (rank 0).  Keys beyond the basic contract:
   roofline      achieved / peak HBM bandwidth of the dominant op (backward), timed with
                 CUDA events inside the timed region
+  per_config    (N = 1) every benchmark configuration c1 ... c5 in the same run: eager and
+                CUDA-graph-replayed ms per step, GB/s of algorithmic bytes, fraction of the
+                measured and of the nominal peak, forward / backward split, the kernel plans;
+                `worst_frac` is the smallest fraction of the measured peak among them
   cpu_baseline  the oracle's fp32 port of the reference CPU functors, timed on the host
-  e2e           the same metric through the public API with pinned HOST buffers: each
-                step copies x and dy to the device and dgamma / dbeta back
+  e2e           the same metric through the public API with pinned HOST buffers: each step
+                copies x and dy to the device and y, dx, dgamma and dbeta back
   clocks        nvidia-smi SM clocks and throttle reasons sampled during the timed region
 
-`--impl reference` times the CPU port alone (the reference's own GPU op needs
-TensorFlow headers, which this environment does not have).
+`--impl reference` times the CPU port alone (the reference's own fused op and the Keras /
+tfa composites need TensorFlow, which this environment does not have).
 """
 from __future__ import annotations
 
@@ -35,13 +43,14 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# DRAM traffic of one backward launch (dram__bytes_read + dram__bytes_write) taken from the
-# ncu capture summarised in profiles/rows_c2_ncu_full.md: 370.9 MB for 16384 rows of c2,
-# i.e. 22 640 bytes per row (traffic grows in proportion to the rows).  Only known for c2.
-NCU_BWD_TRAFFIC_BYTES_PER_ROW = {"c2": 370.93e6 / 16384}
+# DRAM traffic (dram__bytes_read + dram__bytes_write) of one launch of the dominant backward
+# kernel, per row / batch item, from ncu captures of reduced batches (traffic grows in
+# proportion to the batch).  c2: 370.9 MB for 16384 rows.
+NCU_BWD_TRAFFIC_BYTES_PER_ENTRY = {"c2": 370.93e6 / 16384}
 
 NOMINAL_PEAK_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
+CONFIGS = ("c1", "c2", "c3a", "c3b", "c3c", "c4", "c5")
 
 
 def parse_args():
@@ -51,17 +60,21 @@ def parse_args():
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--workload", default="c2")
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    p.add_argument("--scaling", default="auto", choices=["auto", "weak", "strong"],
+                   help="N > 1: 'strong' (default) shards the fixed global batch, 'weak' gives every "
+                        "rank a full batch")
     p.add_argument("--batch", type=int, default=0,
-                   help="override the per-GPU batch extent (rows / batch items); used for small "
+                   help="override the global batch extent (rows / batch items); used for small "
                         "profiler captures, not for reported numbers")
     p.add_argument("--graph", action="store_true",
-                   help="replay the timed steps from a CUDA graph (removes host launch overhead; "
-                        "meant for the small workloads c1 / c3c)")
+                   help="N = 1: report the CUDA-graph replay of the steps as the headline instead of "
+                        "the eager launches")
     p.add_argument("--collective", default="fused-async", choices=["fused-async", "fused", "nccl"],
                    help="N > 1: 'fused' exchanges dgamma|dbeta inside the last backward kernel over "
                         "peer memory; 'fused-async' pushes there and completes the exchange on a "
                         "side stream while the next forward runs; 'nccl' is a separate NCCL all-reduce")
+    p.add_argument("--configs", default="all",
+                   help="N = 1: comma-separated configurations for per_config ('all', 'none', or e.g. c1,c3c)")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     return p.parse_args()
@@ -74,6 +87,31 @@ def measured_peak():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return FALLBACK_PEAK_GBS, "fallback"
+
+
+def scaling_mode(args, world):
+    if args.scaling != "auto":
+        return args.scaling
+    return "strong"
+
+
+def workload_config(w, args, world):
+    """The `config` object; a function of the command line only, so that both arms of one
+    (N, workload) pair print the same one."""
+    mode = scaling_mode(args, world)
+    per_gpu = w.N if mode == "weak" else -(-w.N // world)
+    return {
+        "workload": f"{w.name}: {'LayerNorm' if w.op == 'ln' else 'InstanceNorm ' + w.data_format} "
+                    f"{w.dtype} {list(w.shape())} global batch, eps={w.eps}, fwd+bwd",
+        "per_gpu_batch": per_gpu, "global_batch": w.N * (world if mode == "weak" else 1),
+        "parallelism": f"dp{world}",
+        "collective": ("none" if world == 1 else
+                       "all-reduce of dgamma|dbeta fused into the column-reduce kernel (peer memory)"
+                       if args.collective == "fused" else
+                       "dgamma|dbeta pushed to peers by the column-reduce kernel, summed on a side stream"
+                       if args.collective == "fused-async" else "NCCL all_reduce(dgamma|dbeta)"),
+        "l2": "inputs larger than L2; buffer sets rotated",
+    }
 
 
 # ---------------------------------------------------------------------------
@@ -112,17 +150,18 @@ def cpu_port_time(w, x, dy, gamma, beta, budget_s=12.0, max_reps=5):
     return min(times), len(times)
 
 
-def cpu_sample(w, rows_cap_bytes=600e6):
+def cpu_sample(w, cap_bytes=600e6):
     """A bounded slice of the workload for the CPU arm: whole batch entries, at most
     ~600 MB of activations."""
     from atex_b200 import testing as T
     per_entry = w.D * w.C * T.ELEM_SIZE[w.dtype] if w.op == "in" else w.D * T.ELEM_SIZE[w.dtype]
-    n = int(max(1, min(w.N, rows_cap_bytes // (2 * per_entry))))
-    return n
+    return int(max(1, min(w.N, cap_bytes // (2 * per_entry))))
 
 
 def run_reference_arm(args, rank, world):
-    """`--impl reference`: the CPU port on rank 0; other ranks exit quietly."""
+    """`--impl reference`: the CPU port on rank 0, on the arm's own workload and step count;
+    other ranks exit quietly.  Every step is one pass over a bounded sample of the global
+    batch, sized from a calibration pass so that warm-up + steps stay within ~90 s."""
     if rank != 0:
         return
     from atex_b200 import testing as T
@@ -131,29 +170,41 @@ def run_reference_arm(args, rank, world):
     w = T.WORKLOADS[args.workload]
     if args.batch:
         w = T.scaled(w, args.batch)
-    n = cpu_sample(w)
-    ws = T.scaled(w, n)
-    x, dy = T.make_activations(ws)
+    mode = scaling_mode(args, world)
     gamma, beta = T.make_params(w)
     # torchrun exports OMP_NUM_THREADS=1: ask for every core explicitly
     cores = oracle.set_num_threads(os.cpu_count() or 1)
+    steps = max(1, args.steps)
+    warmup = max(0, args.warmup)
+    # calibration on a small slice -> entries per step that fit the budget
+    n0 = max(1, min(w.N, cpu_sample(w, cap_bytes=64e6)))
+    w0 = T.scaled(w, n0)
+    x0, dy0 = T.make_activations(w0)
+    arrs0 = _cpu_arrays(w0, x0, dy0, gamma, beta)
+    cpu_port_once(w0, *arrs0)
+    per_entry_s = min(cpu_port_once(w0, *arrs0) for _ in range(2)) / n0
+    budget_s = 90.0
+    n = int(budget_s / ((steps + warmup) * per_entry_s))
+    n = max(1, min(n, cpu_sample(w), w.N))
+    ws = T.scaled(w, n)
+    x, dy = T.make_activations(ws)
     arrs = _cpu_arrays(ws, x, dy, gamma, beta)
-    for _ in range(max(1, min(args.warmup, 3))):
+    for _ in range(warmup):
         cpu_port_once(ws, *arrs)
-    steps = max(1, min(args.steps, 10))
     t0 = time.perf_counter()
     for _ in range(steps):
         cpu_port_once(ws, *arrs)
     per_step = (time.perf_counter() - t0) / steps
     gbs = ws.algorithmic_bytes() / per_step / 1e9
-    sample = f"{n} of {w.N} batch entries of {w.name} per step, fwd+bwd, fp32 OpenMP port"
+    sample = (f"{n} of {w.N} batch entries of {w.name} per step, fwd+bwd, fp32 OpenMP port of the "
+              "reference CPU functors")
     line = {
         "impl": "reference",
         "metric": "norm_fwd_bwd_hbm_gbps", "value": gbs, "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
-        "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": args.scaling,
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+        "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": mode,
         "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
-        "config": workload_config(w, args, 1),
+        "config": workload_config(w, args, world),
         "gelem_per_s": ws.elements / per_step / 1e9,
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -161,21 +212,6 @@ def run_reference_arm(args, rank, world):
                 "not installed; this arm is the oracle's fp32 port of the reference CPU functors",
     }
     print(json.dumps(line), flush=True)
-
-
-def workload_config(w, args, world):
-    return {
-        "workload": f"{w.name}: {'LayerNorm' if w.op == 'ln' else 'InstanceNorm ' + w.data_format} "
-                    f"{w.dtype} {list(w.shape())} per GPU, eps={w.eps}, fwd+bwd",
-        "per_gpu_batch": w.N, "global_batch": w.N * (world if args.scaling == "weak" else 1),
-        "parallelism": f"dp{world}",
-        "collective": ("none" if world == 1 else
-                       "all-reduce of dgamma|dbeta fused into the column-reduce kernel (peer memory)"
-                       if args.collective == "fused" else
-                       "dgamma|dbeta pushed to peers by the column-reduce kernel, summed on a side stream"
-                       if args.collective == "fused-async" else "NCCL all_reduce(dgamma|dbeta)"),
-        "l2": "inputs larger than L2; buffer sets rotated",
-    }
 
 
 # ---------------------------------------------------------------------------
@@ -238,6 +274,214 @@ class ClockSampler:
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
+class Runner:
+    """Forward + backward of one workload on one device over rotating, preallocated buffer
+    sets (enough of them that consecutive steps never find their inputs in the 126 MB L2).
+    Outputs are preallocated too, so a steady-state step allocates nothing."""
+
+    def __init__(self, w, x0, dy0, gamma, beta, exchange=None, deferred=False, nccl=False):
+        import torch
+        import atex_b200 as A
+        from atex_b200 import testing as T
+        self.torch, self.A, self.w = torch, A, w
+        self.dev = x0.device
+        self.gamma, self.beta = gamma, beta
+        n_local = x0.shape[0]
+        self.wl = T.scaled(w, n_local)
+        F = w.features
+        set_bytes = 2 * self.wl.elements * T.ELEM_SIZE[w.dtype]
+        self.nsets = max(1, min(8, int(-(-400e6 // max(set_bytes, 1)))))
+        self.xs, self.dys = [x0], [dy0]
+        for k in range(1, self.nsets):
+            self.xs.append(x0.roll(k, 0).contiguous())
+            self.dys.append(dy0.roll(k, 0).contiguous())
+        self.ys = [torch.empty_like(x0) for _ in range(self.nsets)]
+        self.dxs = [torch.empty_like(x0) for _ in range(self.nsets)]
+        R = self.wl.stat_rows
+        stat_shape = (R,) if w.op == "ln" else (n_local, w.C)
+        self.stats = [(torch.empty(stat_shape, dtype=torch.float32, device=self.dev),
+                       torch.empty(stat_shape, dtype=torch.float32, device=self.dev))
+                      for _ in range(self.nsets)]
+        # dgamma and dbeta are written next to each other, so one all-reduce covers both
+        self.grad_buf = torch.empty(2 * F, dtype=torch.float32, device=self.dev)
+        self.grad_views = (self.grad_buf[:F], self.grad_buf[F:])
+        self.exchange, self.deferred, self.nccl = exchange, deferred and exchange is not None, nccl
+        self.side = torch.cuda.Stream(device=self.dev) if self.deferred else None
+        self.fin_ev = [torch.cuda.Event() for _ in range(4)]
+        self.push_ev = [torch.cuda.Event() for _ in range(4)]
+        self.pending = 0
+
+    def fwd(self, i, x=None):
+        k = i % self.nsets
+        w = self.w
+        x = self.xs[k] if x is None else x
+        if w.op == "ln":
+            return self.A.fused_layer_norm_op(x, self.gamma, self.beta, axis=[-1], epsilon=w.eps,
+                                              out=self.ys[k], out_stats=self.stats[k])
+        return self.A.fused_instance_norm_op(x, self.gamma, self.beta, data_format=w.data_format,
+                                             epsilon=w.eps, out=self.ys[k], out_stats=self.stats[k])
+
+    def bwd(self, i, x=None, dy=None, exchange=True):
+        k = i % self.nsets
+        w = self.w
+        x = self.xs[k] if x is None else x
+        dy = self.dys[k] if dy is None else dy
+        m, s = self.stats[k]
+        ex = self.exchange if exchange else None
+        if w.op == "ln":
+            return self.A.fused_layer_norm_grad_op(dy, x, self.gamma, m, s, axis=[-1],
+                                                   out_grads=self.grad_views, grad_exchange=ex,
+                                                   out=self.dxs[k])
+        return self.A.fused_instance_norm_grad_op(dy, x, self.gamma, m, s, data_format=w.data_format,
+                                                  out_grads=self.grad_views, grad_exchange=ex,
+                                                  out=self.dxs[k])
+
+    def step(self, i, ev=None, x=None, dy=None, exchange=True):
+        torch = self.torch
+        self.fwd(i, x)
+        if ev is not None:
+            ev[0].record()
+        main = torch.cuda.current_stream()
+        deferred = self.deferred and exchange
+        if deferred and self.pending > 1:
+            # a push of epoch e needs this rank's finish of e - 2 (four receive slots)
+            main.wait_event(self.fin_ev[(self.pending - 2) % 4])
+        self.bwd(i, x, dy, exchange)
+        if ev is not None:
+            ev[1].record()
+        if deferred:
+            k = self.pending % 4
+            self.push_ev[k].record(main)
+            self.side.wait_event(self.push_ev[k])
+            self.exchange.finish(self.grad_views[0], self.grad_views[1], stream=self.side)
+            self.fin_ev[k].record(self.side)
+            self.pending += 1
+        if self.nccl and exchange:
+            import torch.distributed as dist
+            dist.all_reduce(self.grad_buf)
+
+    def drain(self):
+        if self.deferred and self.pending > 0:
+            self.torch.cuda.current_stream().wait_event(self.fin_ev[(self.pending - 1) % 4])
+
+
+def _time_loop(torch, fn, n, sync):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    e0.record()
+    for i in range(n):
+        fn(i)
+    e1.record()
+    sync()
+    return e0.elapsed_time(e1) / n
+
+
+def _graph_ms(torch, body, nsets, steps):
+    """ms per body(i) when `nsets` consecutive calls are replayed from one CUDA graph."""
+    cap = torch.cuda.Stream()
+    with torch.cuda.stream(cap):
+        for i in range(nsets):
+            body(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=cap):
+        for i in range(nsets):
+            body(i)
+    reps = max(2, -(-steps // nsets))
+    for _ in range(2):
+        graph.replay()
+    ms = _time_loop(torch, lambda _i: graph.replay(), reps, torch.cuda.synchronize) / nsets
+    del graph
+    return ms
+
+
+def device_inputs(w, dev, seed):
+    """x, dy of the workload generated on the device (same distributions as the host
+    generator of atex_b200.testing; used for the per-configuration sweep, whose inputs never
+    leave the GPU)."""
+    import torch
+    from atex_b200 import testing as T
+    g = torch.Generator(device=dev).manual_seed(seed)
+    shape = w.shape()
+    dt = T.TORCH_DTYPE[w.dtype]
+    x = torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+    if w.x_kind == "row_offset":
+        x.mul_(4.0).add_(torch.randn((shape[0], 1), generator=g, device=dev))
+    elif w.x_kind == "mean2_std3":
+        x.mul_(3.0).add_(2.0)
+    elif w.x_kind == "channel_scale":
+        s = torch.rand(w.C, generator=g, device=dev) * 1.5 + 0.5
+        x.mul_(s.reshape((1, w.C) + (1,) * (len(shape) - 2)) if w.channel_first else s)
+    xo = x.to(dt)
+    del x
+    dy = torch.randn(shape, generator=g, device=dev, dtype=torch.float32).to(dt)
+    return xo, dy
+
+
+def measure_config(name, dev, peak, steps=20, host_calls=0):
+    """One entry of `per_config`: the workload's forward + backward on one GPU, launched
+    eagerly through the public API and replayed from CUDA graphs."""
+    import torch
+    from atex_b200 import _lib
+    from atex_b200 import testing as T
+    w = T.WORKLOADS[name]
+    gamma_h, beta_h = T.make_params(w)
+    gamma, beta = gamma_h.to(dev), beta_h.to(dev)
+    x, dy = device_inputs(w, dev, 77 + w.index)
+    r = Runner(w, x, dy, gamma, beta)
+    sync = torch.cuda.synchronize
+    for i in range(3):
+        r.step(i)
+    eager_ms = _time_loop(torch, r.step, steps, sync)
+    graph_ms = _graph_ms(torch, r.step, r.nsets, steps)
+    fwd_ms = _graph_ms(torch, r.fwd, r.nsets, steps)
+    bwd_ms = _graph_ms(torch, r.bwd, r.nsets, steps)
+    s = T.ELEM_SIZE[w.dtype]
+    F, R, E = w.features, w.stat_rows, w.elements
+    fwd_bytes = 2 * E * s + 2 * F * 4 + 2 * R * 4
+    bwd_bytes = 3 * E * s + 3 * F * 4 + 2 * R * 4
+    total = w.algorithmic_bytes()
+    gbs = total / (graph_ms * 1e-3) / 1e9
+    opn = 0 if w.op == "ln" else 2
+    code = {"f32": 0, "f16": 1, "bf16": 2}[w.dtype]
+    out = {
+        "workload": f"{'LayerNorm' if w.op == 'ln' else 'InstanceNorm ' + w.data_format} {w.dtype} {list(w.shape())}",
+        "eager_ms_per_step": eager_ms, "graph_ms_per_step": graph_ms,
+        "gbps": gbs, "gelem_per_s": E / (graph_ms * 1e-3) / 1e9,
+        "frac_of_measured": gbs / peak, "frac_of_nominal_8000": gbs / NOMINAL_PEAK_GBS,
+        "eager_frac_of_measured": total / (eager_ms * 1e-3) / 1e9 / peak,
+        "fwd": {"graph_ms": fwd_ms, "gbps": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
+                "frac_of_measured": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak,
+                "plan": _lib.describe_plan(opn, code, w.N, w.C, w.D, int(w.channel_first))},
+        "bwd": {"graph_ms": bwd_ms, "gbps": bwd_bytes / (bwd_ms * 1e-3) / 1e9,
+                "frac_of_measured": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak,
+                "plan": _lib.describe_plan(opn + 1, code, w.N, w.C, w.D, int(w.channel_first))},
+        "algorithmic_bytes": total, "buffer_sets": r.nsets,
+    }
+    if name == "c4":
+        # the two-phase channels-last kernels move x twice forward and x, dy twice backward
+        # (one batch item exceeds L2): 8 tensor passes for the 5 counted
+        moved = 8 * E * s
+        out["frac_of_measured_by_bytes_moved_8_passes"] = moved / (graph_ms * 1e-3) / 1e9 / peak
+    if host_calls:
+        # host cost of one op call through the public API (launches are asynchronous; the
+        # problem is small enough that the GPU keeps up with the issue rate)
+        sync()
+        t0 = time.perf_counter()
+        for i in range(host_calls):
+            r.fwd(i)
+        t1 = time.perf_counter()
+        for i in range(host_calls):
+            r.bwd(i)
+        t2 = time.perf_counter()
+        sync()
+        out["host_us_per_call"] = {"fwd": (t1 - t0) / host_calls * 1e6, "bwd": (t2 - t1) / host_calls * 1e6,
+                                   "calls": host_calls}
+    del r, x, dy
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -250,7 +494,6 @@ def main():
     import torch
     import torch.distributed as dist
 
-    import atex_b200 as A
     from atex_b200 import _lib, sharding
     from atex_b200 import testing as T
 
@@ -262,85 +505,31 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
+    mode = scaling_mode(args, world)
+    peak, peak_kind = measured_peak()
 
     w = T.WORKLOADS[args.workload]
     if args.batch:
         w = T.scaled(w, args.batch)
-    if args.scaling == "weak":
-        a, b = rank * w.N, (rank + 1) * w.N
-        wl = w
-        x_h, dy_h = T.make_activations(T.scaled(w, world * w.N), a, b, pin=True)
-    else:
-        a, b = sharding.shard_range(w.N, rank, world)
-        wl = T.scaled(w, b - a)
-        x_h, dy_h = T.make_activations(w, a, b, pin=True)
     gamma_h, beta_h = T.make_params(w)
     gamma, beta = gamma_h.to(dev), beta_h.to(dev)
     F = w.features
 
-    # Resident inputs: enough rotating sets that consecutive steps never find their
-    # inputs in the 126 MB L2.
-    set_bytes = 2 * wl.elements * T.ELEM_SIZE[w.dtype]
-    nsets = max(1, min(8, int(-(-400e6 // set_bytes))))
-    xs = [x_h.to(dev)]
-    dys = [dy_h.to(dev)]
-    for k in range(1, nsets):
-        xs.append(xs[0].roll(k, 0).contiguous())
-        dys.append(dys[0].roll(k, 0).contiguous())
-    # dgamma and dbeta are written next to each other, so one all-reduce covers both
-    grad_buf = torch.empty(2 * F, dtype=torch.float32, device=dev)
-    grad_views = (grad_buf[:F], grad_buf[F:])
+    def shard_inputs(kind):
+        if kind == "weak":
+            return T.make_activations(T.scaled(w, world * w.N), rank * w.N, (rank + 1) * w.N, pin=True)
+        a, b = sharding.shard_range(w.N, rank, world)
+        return T.make_activations(w, a, b, pin=True)
 
-    exchange = None
-    deferred = args.collective == "fused-async"
-    if world > 1 and args.collective != "nccl" and F % 2 == 0:
-        exchange = sharding.GradExchange(F, dev, deferred=deferred)
-    side = torch.cuda.Stream(device=dev) if (exchange is not None and deferred) else None
-    fin_ev = [torch.cuda.Event() for _ in range(4)]
-    push_ev = [torch.cuda.Event() for _ in range(4)]
-    pending = {"n": 0}
-    if w.op == "ln":
-        def fwd(x):
-            return A.fused_layer_norm_op(x, gamma, beta, axis=[-1], epsilon=w.eps)
+    x_h, dy_h = shard_inputs(mode)
 
-        def bwd(dy, x, m, s):
-            return A.fused_layer_norm_grad_op(dy, x, gamma, m, s, axis=[-1], out_grads=grad_views,
-                                              grad_exchange=exchange)
-    else:
-        def fwd(x):
-            return A.fused_instance_norm_op(x, gamma, beta, data_format=w.data_format, epsilon=w.eps)
-
-        def bwd(dy, x, m, s):
-            return A.fused_instance_norm_grad_op(dy, x, gamma, m, s, data_format=w.data_format,
-                                                 out_grads=grad_views, grad_exchange=exchange)
-
-    def step(i, ev=None):
-        x, dy = xs[i % nsets], dys[i % nsets]
-        y, m, s = fwd(x)
-        if ev is not None:
-            ev[0].record()
-        main = torch.cuda.current_stream()
-        if side is not None and pending["n"] > 1:
-            # receive slots are reused every fourth step: staying at most two finishes
-            # ahead keeps every slot's readers done before it is overwritten
-            main.wait_event(fin_ev[(pending["n"] - 2) % 4])
-        dx, dg, db = bwd(dy, x, m, s)
-        if ev is not None:
-            ev[1].record()
-        if side is not None:
-            k = pending["n"] % 4
-            push_ev[k].record(main)
-            side.wait_event(push_ev[k])
-            exchange.finish(grad_views[0], grad_views[1], stream=side)
-            fin_ev[k].record(side)
-            pending["n"] += 1
-        if world > 1 and exchange is None:
-            dist.all_reduce(grad_buf)
-        return y, dx, dg, db
-
-    def drain():
-        if side is not None and pending["n"] > 0:
-            torch.cuda.current_stream().wait_event(fin_ev[(pending["n"] - 1) % 4])
+    def make_runner(xh, dyh):
+        exchange = None
+        deferred = args.collective == "fused-async"
+        if world > 1 and args.collective != "nccl" and F % 2 == 0:
+            exchange = sharding.GradExchange(F, dev, deferred=deferred)
+        return Runner(w, xh.to(dev), dyh.to(dev), gamma, beta, exchange=exchange, deferred=deferred,
+                      nccl=(world > 1 and exchange is None))
 
     def barrier():
         torch.cuda.synchronize()
@@ -348,34 +537,34 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(max(args.warmup, 3)):
-        step(i)
+    def max_over_ranks(ms):
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(r, K, exchange=True):
+        """ms per step of K eager steps, max over ranks (barrier + synchronize on both sides)."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(K):
+            r.step(i, exchange=exchange)
+        if exchange:
+            r.drain()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1)) / K
+
+    r = make_runner(x_h, dy_h)
+    wl = r.wl
+    W = max(args.warmup, 3)
+    for i in range(W):
+        r.step(i)
+    r.drain()
     barrier()
 
     K = args.steps
-    graph_ms = None
-    if args.graph and world == 1:
-        # One graph holds `nsets` consecutive steps (one per rotating buffer set).
-        side = torch.cuda.Stream()
-        with torch.cuda.stream(side):
-            for i in range(nsets):
-                step(i)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            for i in range(nsets):
-                step(i)
-        reps = max(1, -(-K // nsets))
-        for _ in range(3):
-            graph.replay()
-        torch.cuda.synchronize()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        for _ in range(reps):
-            graph.replay()
-        g1.record()
-        torch.cuda.synchronize()
-        graph_ms = g0.elapsed_time(g1) / (reps * nsets)
     mids = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -394,66 +583,121 @@ def main():
     for i in range(K):
         if i % stride == stride - 1:
             starts[i].record()
-            step(i, mids[i])
+            r.step(i, mids[i])
         else:
-            step(i)
-    drain()
+            r.step(i)
+    r.drain()
     e1.record()
     barrier()
     t_wall1 = time.perf_counter()
     launches = lib.nvn_launch_count() - launches0
     clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
-    ms_total = e0.elapsed_time(e1)
-    t_ms = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
-    ms_per_step = float(t_ms.item()) / K
+    ms_per_step = max_over_ranks(e0.elapsed_time(e1)) / K
     eager_ms_per_step = ms_per_step
-    if graph_ms is not None:
-        ms_per_step = graph_ms
     fwd_ms = statistics.mean(starts[i].elapsed_time(mids[i][0]) for i in sampled)
     bwd_ms = statistics.mean(mids[i][0].elapsed_time(mids[i][1]) for i in sampled)
+    graph_ms = None
+    if args.graph and world == 1:
+        graph_ms = _graph_ms(torch, r.step, r.nsets, K)
+        ms_per_step = graph_ms
 
-    # ---- e2e: pinned host buffers in, parameter gradients out, every step ----
+    # ---- N > 1: compute / exchange split, correctness of the exchange, weak sub-record ----
+    split = dp_check = weak = None
+    if world > 1:
+        local_ms = timed(r, K, exchange=False)   # the same shard without any exchange
+        split = {"step_ms": eager_ms_per_step, "compute_ms": local_ms,
+                 "exchange_ms": eager_ms_per_step - local_ms,
+                 "fwd_interval_ms": max_over_ranks(fwd_ms), "bwd_interval_ms": max_over_ranks(bwd_ms),
+                 "note": "compute = the same fwd+bwd on this rank's shard with the local column "
+                         "reduction only; exchange = what the step costs on top of it"}
+        # exchanged [dgamma | dbeta] against one NCCL all-reduce of the local vectors
+        r.step(0)
+        r.drain()
+        torch.cuda.synchronize()
+        got = r.grad_buf.clone()
+        r.step(0, exchange=False)
+        torch.cuda.synchronize()
+        ref = r.grad_buf.clone()
+        dist.all_reduce(ref)
+        torch.cuda.synchronize()
+        denom = float(ref.abs().max().item()) or 1.0
+        err = float((got - ref).abs().max().item()) / denom
+        same = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(same, got)
+        identical = all(torch.equal(same[0], t) for t in same)
+        ok = torch.tensor([1 if (err <= 1e-5 and identical and lib.nvn_device_status() == 0) else 0],
+                          device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        dp_check = {"status": "ok" if int(ok.item()) == 1 else "fail", "max_rel_err_vs_nccl": err,
+                    "bit_identical_on_all_ranks": identical}
+
+    # ---- e2e: pinned host buffers in; y, dx and the parameter gradients out, every step ----
     e2e = None
     if not args.no_e2e:
-        xd, dyd = torch.empty_like(xs[0]), torch.empty_like(dys[0])
+        xd, dyd = torch.empty_like(r.xs[0]), torch.empty_like(r.dys[0])
+        y_h = torch.empty_like(x_h).pin_memory()
+        dx_h = torch.empty_like(x_h).pin_memory()
         out_h = torch.empty(2 * F, dtype=torch.float32).pin_memory()
 
-        def e2e_step():
+        def e2e_step(i):
             xd.copy_(x_h, non_blocking=True)
             dyd.copy_(dy_h, non_blocking=True)
-            y, m, s = fwd(xd)
-            dx, dg, db = bwd(dyd, xd, m, s)
-            if side is not None:
-                k = pending["n"] % 4
-                push_ev[k].record(torch.cuda.current_stream())
-                side.wait_event(push_ev[k])
-                exchange.finish(grad_views[0], grad_views[1], stream=side)
-                fin_ev[k].record(side)
-                pending["n"] += 1
-                drain()
-            if world > 1 and exchange is None:
-                dist.all_reduce(grad_buf)
-            out_h.copy_(grad_buf, non_blocking=True)
+            r.step(0, x=xd, dy=dyd)
+            r.drain()
+            y_h.copy_(r.ys[0], non_blocking=True)
+            dx_h.copy_(r.dxs[0], non_blocking=True)
+            out_h.copy_(r.grad_buf, non_blocking=True)
 
         Ke = max(3, min(K, 20))
-        for _ in range(3):
-            e2e_step()
-        barrier()
+        for i in range(3):
+            e2e_step(i)
         s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
         s0.record()
-        for _ in range(Ke):
-            e2e_step()
+        for i in range(Ke):
+            e2e_step(i)
         s1.record()
         barrier()
-        te = torch.tensor([s0.elapsed_time(s1)], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e_ms = float(te.item()) / Ke
-        e2e = {"value": world * wl.algorithmic_bytes() / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-               "h2d_bytes_per_step": 2 * wl.elements * T.ELEM_SIZE[w.dtype],
-               "d2h_bytes_per_step": 2 * F * 4, "ms_per_step": e2e_ms, "steps": Ke}
+        e2e_ms = max_over_ranks(s0.elapsed_time(s1)) / Ke
+        esz = T.ELEM_SIZE[w.dtype]
+        e2e = {"value": (world if mode == "weak" else 1) * w.algorithmic_bytes() / (e2e_ms * 1e-3) / 1e9,
+               "unit": "GB/s",
+               "h2d_bytes_per_step": 2 * wl.elements * esz,
+               "d2h_bytes_per_step": 2 * wl.elements * esz + 2 * F * 4,
+               "ms_per_step": e2e_ms, "steps": Ke,
+               "copies": "per rank and step: x, dy host->device; y, dx, dgamma|dbeta device->host (pinned)"}
+
+    # ---- N > 1: the weak-scaling arrangement (every rank a full batch) as a sub-record ----
+    if world > 1 and mode == "strong" and args.scaling == "auto":
+        del r
+        torch.cuda.empty_cache()
+        xw, dyw = shard_inputs("weak")
+        rw = make_runner(xw, dyw)
+        for i in range(3):
+            rw.step(i)
+        rw.drain()
+        wms = timed(rw, K)
+        weak = {"scaling": "weak", "per_gpu_batch": w.N, "global_batch": w.N * world,
+                "ms_per_step": wms,
+                "value": world * w.algorithmic_bytes() / (wms * 1e-3) / 1e9, "unit": "GB/s"}
+        del rw
+        torch.cuda.empty_cache()
+        r = None
+
+    # ---- every configuration in the same run (single GPU only) ----
+    per_config = None
+    worst = None
+    if world == 1 and args.configs != "none" and not args.batch:
+        names = CONFIGS if args.configs == "all" else tuple(c for c in args.configs.split(",") if c in CONFIGS)
+        del r
+        torch.cuda.empty_cache()
+        per_config = {}
+        for name in names:
+            per_config[name] = measure_config(name, dev, peak, steps=20,
+                                              host_calls=500 if name == "c1" else 0)
+        if per_config:
+            worst_name = min(per_config, key=lambda n: per_config[n]["frac_of_measured"])
+            worst = {"config": worst_name, "frac_of_measured": per_config[worst_name]["frac_of_measured"]}
 
     if rank != 0:
         if world > 1:
@@ -461,9 +705,9 @@ def main():
             dist.destroy_process_group()
         return
 
-    peak, peak_kind = measured_peak()
-    total_bytes = world * wl.algorithmic_bytes()
-    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+    global_bytes = (world if mode == "weak" else 1) * w.algorithmic_bytes()
+    global_elems = (world if mode == "weak" else 1) * w.elements
+    value = global_bytes / (ms_per_step * 1e-3) / 1e9
     s = T.ELEM_SIZE[w.dtype]
     R = wl.stat_rows
     bwd_bytes = 3 * wl.elements * s + 3 * F * 4 + 2 * R * 4
@@ -475,8 +719,8 @@ def main():
     roofline = {
         "bound": "hbm", "achieved": bwd_gbs, "peak": peak, "unit": "GB/s", "frac": bwd_gbs / peak,
         "peak_kind": peak_kind,
-        "traffic": (NCU_BWD_TRAFFIC_BYTES_PER_ROW[w.name] * wl.N
-                    if w.name in NCU_BWD_TRAFFIC_BYTES_PER_ROW else None),
+        "traffic": (NCU_BWD_TRAFFIC_BYTES_PER_ENTRY[w.name] * wl.N
+                    if w.name in NCU_BWD_TRAFFIC_BYTES_PER_ENTRY else None),
         "kernel": f"{w.op}_bwd: " + _lib.describe_plan(opn + 1, code, wl.N, w.C, w.D, int(w.channel_first)),
         "algorithmic_bytes_per_launch": bwd_bytes, "ms_per_launch": bwd_ms,
         "launches_timed": len(sampled),
@@ -501,11 +745,11 @@ def main():
 
     line = {
         "metric": "norm_fwd_bwd_hbm_gbps", "value": value, "unit": "GB/s", "n_gpus": world,
-        "steps": K, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+        "steps": K, "warmup": W, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": mode, "vs_baseline": None,
         "dtype": w.dtype, "data": "synthetic",
         "config": workload_config(w, args, world),
-        "gelem_per_s": world * wl.elements / (ms_per_step * 1e-3) / 1e9,
+        "gelem_per_s": global_elems / (ms_per_step * 1e-3) / 1e9,
         "pct_of_nominal_8000": 100.0 * (value / world) / NOMINAL_PEAK_GBS,
         "pct_of_measured_peak": 100.0 * (value / world) / peak,
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
@@ -513,6 +757,15 @@ def main():
     }
     if graph_ms is not None:
         line["timing"] = "CUDA-graph replay of the steps; eager launch path: %.4f ms/step" % eager_ms_per_step
+    if split is not None:
+        line["split"] = split
+        line["dp_check"] = dp_check["status"]
+        line["dp_check_detail"] = dp_check
+    if weak is not None:
+        line["weak"] = weak
+    if per_config is not None:
+        line["per_config"] = per_config
+        line["worst_frac"] = worst
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -178,9 +178,12 @@ NVN_API int nvn_in_bwd(int dtype, const void* dy, const void* x, const float* ga
  *             the first call
  * in rank order (recv[rank] is this rank's own).  `epoch` must be 1 on the first call and
  * grow by one per call, the same on all ranks; calls of one communicator must not overlap
- * on a GPU.  F must be even.  Device-side waits are bounded: if a peer never shows up the
- * kernel gives up, nvn_device_status() reports NVN_ERR_TIMEOUT and the gradients of that
- * call are undefined.  world == 1 is allowed (pure self-exchange).
+ * on a GPU.  F must be even.  A set of receive buffers is bound to ONE feature count F: the
+ * slot offsets depend on F, so layers with different F need their own buffers and their
+ * own epoch sequence.  Device-side waits are bounded: if a peer never shows up the kernel
+ * gives up (after one time-out per thread, not one per element), nvn_device_status()
+ * reports NVN_ERR_TIMEOUT and the gradients of that call are undefined.  world == 1 is
+ * allowed (pure self-exchange).
  * No counterpart in the reference (its ops are single-device, norm_ops.cc has no
  * collective); this replaces the separate all-reduce of a data-parallel job. */
 #define NVN_DP_MAX_RANKS 16
@@ -196,9 +199,9 @@ typedef struct nvn_dp_comm {
 /* Second half of a deferred exchange (comm->defer was 1 in the backward call of this
  * epoch): waits - bounded - for every rank's push of `comm->epoch` and writes the summed
  * dgamma / dbeta (F floats each).  May run on another stream than the backward call, after
- * it in stream / event order.  The caller must not start the backward call of epoch e + 1
- * on a rank before that rank's nvn_dp_finish of epoch e - 2 has completed (a receive slot
- * is reused every fourth epoch). */
+ * it in stream / event order.  The caller must not start the backward call of epoch e on a
+ * rank before that rank's nvn_dp_finish of epoch e - 2 has completed: there are four receive
+ * slots (epoch mod 4), and a finish that lags its push by L epochs needs 2L of them. */
 NVN_API int nvn_dp_finish(int64_t F, const nvn_dp_comm* comm, float* dgamma, float* dbeta,
                           void* stream);
 

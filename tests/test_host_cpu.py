@@ -11,7 +11,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 import atex_b200 as A
-from atex_b200 import sharding
+from atex_b200 import _lib, sharding
 from atex_b200 import testing as T
 
 
@@ -172,3 +172,63 @@ def test_allreduce_is_identity_without_a_process_group():
     a, b = torch.ones(4), torch.zeros(4)
     ra, rb = sharding.allreduce_param_grads(a, b)
     assert ra is a and rb is b
+
+
+# ---------------------------------------------------------------------------
+# Receive-slot arithmetic of the deferred exchange (host logic of colreduce_dp.cu).
+# A model of the protocol: every rank pushes epoch e into slot e % NUM_SLOTS of every peer
+# and later "finishes" e (reads its own slot rows, which needs every rank's push of e).
+# The contract: a rank pushes e only after its own finish of e - MAX_FINISH_LAG.  The model
+# lets ranks run in random order under that contract and checks that no push ever
+# overwrites a slot whose reader has not finished; with a larger lag the check must fail.
+# ---------------------------------------------------------------------------
+def _simulate_exchange(world, epochs, lag, seed):
+    import random
+    rnd = random.Random(seed)
+    pushed = [0] * world      # highest epoch pushed by rank r
+    finished = [0] * world    # highest epoch finished by rank r
+    slot = [[[0] * world for _ in range(sharding.NUM_SLOTS)] for _ in range(world)]  # [owner][slot][src]
+    while min(finished) < epochs:
+        r = rnd.randrange(world)
+        can_push = pushed[r] < epochs and finished[r] >= pushed[r] + 1 - lag
+        e_fin = finished[r] + 1
+        can_finish = e_fin <= pushed[r] and all(pushed[q] >= e_fin for q in range(world))
+        choices = [c for c, okc in (("push", can_push), ("finish", can_finish)) if okc]
+        if not choices:
+            continue
+        if rnd.choice(choices) == "push":
+            e = pushed[r] + 1
+            for owner in range(world):
+                # the value being overwritten belongs to epoch e - NUM_SLOTS: its reader must be done
+                if finished[owner] < e - sharding.NUM_SLOTS:
+                    return False
+                slot[owner][sharding.slot_of_epoch(e)][r] = e
+            pushed[r] = e
+        else:
+            if any(slot[r][sharding.slot_of_epoch(e_fin)][q] != e_fin for q in range(world)):
+                return False   # a needed value was overwritten before it was read
+            finished[r] = e_fin
+    return True
+
+
+def test_documented_finish_lag_keeps_every_receive_slot_safe():
+    assert sharding.MAX_FINISH_LAG * 2 == sharding.NUM_SLOTS
+    for world in (2, 3, 8):
+        for seed in range(40):
+            assert _simulate_exchange(world, 40, sharding.MAX_FINISH_LAG, seed)
+    assert sharding.push_allowed(3, 1) and not sharding.push_allowed(4, 1)
+
+
+def test_a_longer_finish_lag_overwrites_unread_slots():
+    # lagging the finish by three epochs with four slots is the hazard: some schedule breaks
+    broke = any(not _simulate_exchange(2, 40, 3, seed) for seed in range(200))
+    assert broke
+
+
+def test_grad_exchange_is_bound_to_one_feature_count():
+    ex = sharding.GradExchange.__new__(sharding.GradExchange)
+    ex.features, ex.epoch, ex._comm = 64, 0, _lib.DpComm()
+    ex.next_comm(64)
+    assert ex.epoch == 1
+    with pytest.raises(ValueError):
+        ex.next_comm(128)

@@ -5,8 +5,7 @@ scratch is a fixed array inside the library, shared by all calls on a device.
 
 Called here straight through the C ABI and compared with the regular nvn_ln_bwd on the
 same inputs, twice in a row: the second call finds the first call's data in the shared
-array and must not be disturbed by it.  The file name sorts last on purpose, so a run
-that stops at the first failure has already executed every other test.
+array and must not be disturbed by it.
 """
 import ctypes
 
@@ -23,10 +22,7 @@ NOALLOC_MAX = 16 << 20  # NVN_NOALLOC_SCRATCH_BYTES in include/nvnorms.h
 
 
 def _noalloc(lib):
-    fn = lib.nvn_ln_bwd_noalloc
-    fn.restype = ctypes.c_int
-    fn.argtypes = [ctypes.c_int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp]
-    return fn
+    return lib.nvn_ln_bwd_noalloc   # prototype attached by atex_b200._lib.load()
 
 
 def _inputs(N, D, dtype, seed):
