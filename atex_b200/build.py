@@ -37,6 +37,7 @@ def _units():
     for t, tname in ((0, "f32"), (1, "f16"), (2, "bf16")):
         for b, dname in ((0, "fwd"), (1, "bwd")):
             units.append((f"rows_{tname}_{dname}.o", "rows_inst.cu", [f"-DNVN_T={t}", f"-DNVN_BWD={b}"]))
+    units.append(("rows_wide.o", "rows_wide.cu", []))
     units.append(("twophase.o", "twophase.cu", []))
     units.append(("colreduce.o", "colreduce.cu", []))
     units.append(("colreduce_dp.o", "colreduce_dp.cu", []))

@@ -32,6 +32,7 @@ __global__ void __launch_bounds__(kTX* TY)
   // blockIdx.y selects a slab of rows (a single slab covers all rows)
   const int64_t p_begin = static_cast<int64_t>(blockIdx.y) * slab_rows;
   const int64_t p_end = p_begin + slab_rows < P ? p_begin + slab_rows : P;
+  griddep_launch_dependents();  // the next kernel in the stream may be scheduled early
   griddep_wait();  // the partial rows come from the kernel launched just before
   float s[W];
 #pragma unroll

@@ -45,6 +45,23 @@ struct RowsPlan {
   int partial_rows;  // rows of [2][D] dgamma/dbeta partials the backward kernel writes
 };
 
+// Cluster kernels for LayerNorm rows of thousands of vectors (rows_wide.cu): a row must
+// fill one of the compiled shapes exactly (wide_ok).  Backward leaves `partial_rows` rows of
+// [2][D] dgamma / dbeta partials in RowsArgs::ws.
+struct WidePlan {
+  int grid;
+  int block;
+  int cluster;
+  int vpt;
+  int stages;
+  int partial_rows;
+};
+bool wide_ok(int64_t nvec, bool bwd);
+// `forced`: index of a shape of rows_wide.cu to use instead of the default for the row's
+// width (tuning runs), or -1.
+cudaError_t wide_launch(int dtype, bool bwd, int forced, const RowsArgs& a, cudaStream_t s,
+                        bool dry_run, WidePlan* plan);
+
 // On-chip channels-last InstanceNorm (nlc_onchip.cu): one CTA holds a whole batch item in
 // shared memory.  nlc_onchip_ok: the item fits and C / vector divides the CTA size.  The
 // backward launch leaves per-item (dgamma, dbeta) contributions in colpart[N][2][C].

@@ -59,10 +59,13 @@ constexpr int64_t kHeldRingMinBytes = 64ll << 20;
 //                           warp-per-item kernels
 //   fwd_shape=I bwd_shape=I affine_shape=I   index into the shape tables of nvn_host.h
 //                           (used when that shape is large enough for the row)
+//   wide_fwd=I wide_bwd=I   index into the shape tables of rows_wide.cu (used when the row
+//                           fills that shape)
 struct Variant {
   int wide = 0;  // 0 default, 1 two-phase, 2 cluster
   int nlc = 0;   // 0 default, 1 two-phase, 2 on-chip but no warp-per-item
   int fwd_shape = -1, bwd_shape = -1, affine_shape = -1;
+  int wide_fwd = -1, wide_bwd = -1;
 };
 
 const Variant& variant() {
@@ -85,6 +88,8 @@ const Variant& variant() {
       if (key == "fwd_shape") r.fwd_shape = atoi(val.c_str());
       if (key == "bwd_shape") r.bwd_shape = atoi(val.c_str());
       if (key == "affine_shape") r.affine_shape = atoi(val.c_str());
+      if (key == "wide_fwd") r.wide_fwd = atoi(val.c_str());
+      if (key == "wide_bwd") r.wide_bwd = atoi(val.c_str());
     }
     return r;
   }();
@@ -166,6 +171,8 @@ int fail_cuda(cudaError_t e) {
 // ---------------------------------------------------------------------------
 struct RowProblemPlan {
   bool two_phase;
+  bool wide;       // LayerNorm rows that fill a shape of the split-barrier cluster kernels
+  WidePlan wp;
   size_t off_colscratch;  // slab scratch of the column reduction (0 bytes: none)
   bool has_colscratch;
   bool scalar;     // two-phase variant runs element-wise
@@ -202,6 +209,29 @@ int plan_rows_uncached(int dtype, bool bwd, bool row_affine, int64_t rows, int64
   p->two_phase = p->shape < 0;
   const int table_index = p->shape;  // `table[table_index]` below; p->shape is what the launcher gets
   if (affine_wide && p->shape >= 0) p->shape += kAffineWideBase;
+  // Rows of thousands of vectors that fill a shape of rows_wide.cu take those kernels.
+  if (!row_affine && full && var.wide == 0 && wide_ok(nvec, bwd)) {
+    RowsArgs a = {};
+    a.N = rows;
+    a.D = D;
+    cudaError_t e =
+        wide_launch(dtype, bwd, bwd ? var.wide_bwd : var.wide_fwd, a, nullptr, true, &p->wp);
+    if (e != cudaSuccess) return fail_cuda(e);
+    p->wide = true;
+    p->two_phase = false;
+    size_t woff = 0;
+    if (bwd) {
+      p->colpart_rows = p->wp.partial_rows;
+      p->off_colpart = 0;
+      woff = align_up(static_cast<size_t>(p->colpart_rows) * 2 * D * 4, 256);
+      const size_t sb = colreduce_scratch_bytes(p->colpart_rows, D);
+      p->has_colscratch = sb > 0;
+      p->off_colscratch = woff;
+      woff += sb;
+    }
+    p->bytes = woff;
+    return NVN_OK;
+  }
   const bool clustered = !p->two_phase && table[table_index].cs > 1;
   // Rows that need a cluster but do not fill its shape lose the ring (equal slices) and run
   // with idle lanes; measured on B200 (bf16 widths 20000 ... 200000, fp32 20000 / 50000) the
@@ -355,9 +385,15 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
     a.C = C;
     a.eps = eps;
     a.status = device_status_word();
-    RowsPlan rp;
-    cudaError_t e =
-        rows_fn(dtype, bwd)(row_affine, p.epv, p.shape, a, stream, false, &rp);
+    cudaError_t e;
+    if (p.wide) {
+      WidePlan wp;
+      e = wide_launch(dtype, bwd, bwd ? variant().wide_bwd : variant().wide_fwd, a, stream, false,
+                      &wp);
+    } else {
+      RowsPlan rp;
+      e = rows_fn(dtype, bwd)(row_affine, p.epv, p.shape, a, stream, false, &rp);
+    }
     if (e != cudaSuccess) return fail_cuda(e);
   } else {
     R2Args a = {};
@@ -875,7 +911,10 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
   RowProblemPlan p;
   int st = plan_rows(dtype, bwd, is_in, rows, D, N, is_in ? C : 1, 16, 16, &p);
   if (st != NVN_OK) return st;
-  if (p.two_phase) {
+  if (p.wide) {
+    snprintf(out, out_bytes, "rows wide block=%d vpt=%d cluster=%d stages=%d epv=%d grid=%d",
+             p.wp.block, p.wp.vpt, p.wp.cluster, p.wp.stages, full_epv(dtype), p.wp.grid);
+  } else if (p.two_phase) {
     snprintf(out, out_bytes, "rows two-phase epv=%d chunk=%lld nchunks=%d slices=%d",
              p.scalar ? 1 : full_epv(dtype), static_cast<long long>(p.r2.chunk), p.r2.nchunks,
              p.r2.slices);

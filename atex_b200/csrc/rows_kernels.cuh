@@ -242,6 +242,11 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   constexpr int NE = MathSel<EPV>::NE;
   using P = Pack<T, EPV>;
 
+  // Programmatic dependent launch: the kernel that follows in the stream may be scheduled
+  // as CTAs of this one retire, and this one may have been scheduled while its predecessor
+  // was still running - nothing that the predecessor may have written (activations,
+  // parameters) is read before griddep_wait() below.
+  griddep_launch_dependents();
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(8) uint64_t ring_bars[STAGES];
   __shared__ ReduceSmem<RB, BLOCK> sm;
@@ -277,6 +282,7 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   // y may alias x (in-place forward), so these are not __restrict__.
   const P* xp = reinterpret_cast<const P*>(a.x) + vec0;
   P* yp = reinterpret_cast<P*>(a.out) + vec0;
+  griddep_wait();
 
   E g[PARAMS_IN_REGS ? VPT : 1][NE], b[PARAMS_IN_REGS ? VPT : 1][NE];
   if constexpr (PARAMS_IN_REGS) {
@@ -433,7 +439,8 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   constexpr int NE = MathSel<EPV>::NE;
   using P = Pack<T, EPV>;
 
-  // The column reduction that follows may be scheduled as CTAs of this kernel retire.
+  // The column reduction that follows may be scheduled as CTAs of this kernel retire; this
+  // kernel itself reads nothing its predecessor may have written before griddep_wait().
   griddep_launch_dependents();
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(8) uint64_t ring_bars[STAGES];
@@ -469,6 +476,7 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   const P* __restrict__ xp = reinterpret_cast<const P*>(a.x) + vec0;
   const P* __restrict__ dyp = reinterpret_cast<const P*>(a.dy) + vec0;
   P* __restrict__ dxp = reinterpret_cast<P*>(a.out) + vec0;
+  griddep_wait();
 
   E g[PARAMS_IN_REGS ? VPT : 1][NE];
   E dg[ROW_AFFINE ? 1 : VPT][NE], db[ROW_AFFINE ? 1 : VPT][NE];
@@ -895,14 +903,18 @@ inline cudaError_t launch_rows_exact(const RowsArgs& a, cudaStream_t stream, boo
   cfg.blockDim = dim3(BLOCK, 1, 1);
   cfg.dynamicSmemBytes = ring;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  // programmatic stream serialization: see griddep_wait() in the kernels
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
   if (CS > 1) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = CS;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
   }
   count_launch();
   return cudaLaunchKernelEx(&cfg, kernel, a);
