@@ -43,6 +43,7 @@ def _units():
     units.append(("colreduce_dp.o", "colreduce_dp.cu", []))
     units.append(("nlc_onchip.o", "nlc_onchip.cu", []))
     units.append(("nlc_small.o", "nlc_small.cu", []))
+    units.append(("nlc_stream.o", "nlc_stream.cu", []))
     units.append(("nvnorms_api.o", "nvnorms_api.cu", []))
     units.append(("noalloc.o", "noalloc.cu", []))
     return units

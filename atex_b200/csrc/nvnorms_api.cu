@@ -55,17 +55,20 @@ constexpr int64_t kHeldRingMinBytes = 64ll << 20;
 // NVN_FORCE_VARIANT, read once when the library is first used, holds comma-separated
 // key=value pairs that override the dispatcher for profiler and tuning runs:
 //   wide=twophase|cluster   path of contiguous rows that need a thread-block cluster
-//   nlc=twophase|onchip     channels-last InstanceNorm: skip the on-chip and / or the
-//                           warp-per-item kernels
+//   nlc=twophase|onchip|stream   channels-last InstanceNorm: skip the on-chip and / or
+//                           the warp-per-item kernels; `stream` sends every eligible
+//                           shape, whatever its size, to the persistent kernel
 //   fwd_shape=I bwd_shape=I affine_shape=I   index into the shape tables of nvn_host.h
 //                           (used when that shape is large enough for the row)
 //   wide_fwd=I wide_bwd=I   index into the shape tables of rows_wide.cu (used when the row
 //                           fills that shape)
+//   stream_block=256|512    persistent channels-last kernels: threads per CTA
 struct Variant {
   int wide = 0;  // 0 default, 1 two-phase, 2 cluster
-  int nlc = 0;   // 0 default, 1 two-phase, 2 on-chip but no warp-per-item
+  int nlc = 0;   // 0 default, 1 two-phase, 2 on-chip but no warp-per-item, 3 persistent
   int fwd_shape = -1, bwd_shape = -1, affine_shape = -1;
   int wide_fwd = -1, wide_bwd = -1;
+  int stream_block = 0;  // persistent channels-last kernels: threads per CTA (256 or 512)
 };
 
 const Variant& variant() {
@@ -84,12 +87,14 @@ const Variant& variant() {
       if (eq == std::string::npos) continue;
       const std::string key = item.substr(0, eq), val = item.substr(eq + 1);
       if (key == "wide") r.wide = val == "twophase" ? 1 : (val == "cluster" ? 2 : 0);
-      if (key == "nlc") r.nlc = val == "twophase" ? 1 : (val == "onchip" ? 2 : 0);
+      if (key == "nlc")
+        r.nlc = val == "twophase" ? 1 : (val == "onchip" ? 2 : (val == "stream" ? 3 : 0));
       if (key == "fwd_shape") r.fwd_shape = atoi(val.c_str());
       if (key == "bwd_shape") r.bwd_shape = atoi(val.c_str());
       if (key == "affine_shape") r.affine_shape = atoi(val.c_str());
       if (key == "wide_fwd") r.wide_fwd = atoi(val.c_str());
       if (key == "wide_bwd") r.wide_bwd = atoi(val.c_str());
+      if (key == "stream_block") r.stream_block = atoi(val.c_str());
     }
     return r;
   }();
@@ -433,7 +438,10 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
 // ---------------------------------------------------------------------------
 // Plan for channels-last InstanceNorm (x[n, d, c])
 // ---------------------------------------------------------------------------
+constexpr int kStreamBlock = 512;  // threads per CTA of the persistent channels-last kernels
+
 struct NlcPlan {
+  bool stream;  // persistent kernel: one cooperative launch, item tails kept on chip
   bool scalar;
   bool onchip;  // a batch item fits in shared memory: one launch, one pass over HBM
   bool small;   // small items: one warp per item
@@ -449,6 +457,21 @@ int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, 
   p->scalar = !(vec_ok && C % V == 0);
   // Small items: a warp per item beats a CTA per item below 2048 elements, and is the only
   // one-launch path for channel counts or alignments the vector kernels cannot take.
+  if (vec_ok && allow_onchip && variant().nlc != 1 &&
+      nlc_stream_ok(dtype, N, C, D, variant().nlc == 3)) {
+    p->stream = true;
+    size_t off = nlc_stream_workspace_bytes(bwd, N, C);
+    if (bwd) {
+      p->off_colpart = off;
+      off += align_up(static_cast<size_t>(N) * 2 * C * 4, 256);
+      const size_t sb = colreduce_scratch_bytes(N, C);
+      p->has_colscratch = sb > 0;
+      p->off_colscratch = off;
+      off += sb;
+    }
+    p->bytes = off;
+    return NVN_OK;
+  }
   const bool onchip_ok = vec_ok && allow_onchip && nlc_onchip_ok(dtype, bwd, C, D);
   if (nlc_small_ok(C, D) && (D * C <= 2048 || !onchip_ok)) {
     if (variant().nlc == 0) {
@@ -513,6 +536,23 @@ int run_nlc(int dtype, bool bwd, const void* dy, const void* x, const float* gam
   if (p.bytes > 0 && (ws == nullptr || !aligned(ws, 256) || ws_bytes < p.bytes))
     return NVN_ERR_WORKSPACE;
   char* wsb = static_cast<char*>(ws);
+  if (p.stream) {
+    float* colpart = bwd ? reinterpret_cast<float*>(wsb + p.off_colpart) : nullptr;
+    cudaError_t e = nlc_stream_launch(dtype, bwd, dy, x, gamma, beta, mean_in, ivar_in, N, C, D,
+                                      eps, out, mean, ivar, wsb, colpart, device_status_word(),
+                                      variant().stream_block > 0 ? variant().stream_block : kStreamBlock, stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+    if (bwd) {
+      e = comm != nullptr ? colreduce_allreduce_launch(colpart, N, C, comm, dgamma, dbeta, stream)
+                          : colreduce_launch(colpart, N, C, dgamma, dbeta, stream,
+                                             p.has_colscratch
+                                                 ? reinterpret_cast<float*>(wsb + p.off_colscratch)
+                                                 : nullptr,
+                                             p.has_colscratch ? kColreduceScratchRows : 0);
+      if (e != cudaSuccess) return fail_cuda(e);
+    }
+    return NVN_OK;
+  }
   if (p.onchip || p.small) {
     float* colpart = bwd ? reinterpret_cast<float*>(wsb + p.off_colpart) : nullptr;
     cudaError_t e = p.small
@@ -893,6 +933,12 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
     NlcPlan p;
     int st = plan_nlc(dtype, bwd, N, C, D, true, &p);
     if (st != NVN_OK) return st;
+    if (p.stream) {
+      snprintf(out, out_bytes, "nlc persistent epv=%d consumers=%d ring=6x%dKB",
+               full_epv(dtype), variant().stream_block == 256 ? 256 : kStreamBlock,
+               (variant().stream_block == 256 ? 256 : kStreamBlock) / 16);
+      return NVN_OK;
+    }
     if (p.small) {
       snprintf(out, out_bytes, "nlc warp-per-item block=256");
       return NVN_OK;

@@ -75,6 +75,9 @@ def parse_args():
                         "side stream while the next forward runs; 'nccl' is a separate NCCL all-reduce")
     p.add_argument("--configs", default="all",
                    help="N = 1: comma-separated configurations for per_config ('all', 'none', or e.g. c1,c3c)")
+    p.add_argument("--ref-shapes", action="store_true",
+                   help="N = 1: time forward + backward on the shapes of the reference's own benchmark "
+                        "scripts (fp16) and print them beside its published A100 / H100 figures")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     return p.parse_args()
@@ -482,6 +485,74 @@ def measure_config(name, dev, peak, steps=20, host_calls=0):
     return out
 
 
+# Shapes of the reference's benchmark scripts (benchmark_layer_norm.py:53-63,
+# benchmark_instance_norm.py:58-69) with the "NV" column of its README (ms per training step
+# of the fused op under mixed_float16, eager TensorFlow, wall clock: A100, H100).
+REF_LN_SHAPES = [((10, 10000000), 3.36, 2.36), ((100, 1000000), 2.78, 1.78), ((1000, 100000), 2.81, 1.95),
+                 ((10000, 10000), 4.50, 5.84), ((100000, 1000), 4.32, 4.73), ((1000000, 100), 6.33, 6.26),
+                 ((10000000, 10), 13.82, 10.61), ((4, 400001), 0.59, 0.74), ((4, 10000001), 1.69, 1.15)]
+REF_IN_SHAPES = [(2, 32, 6), (2, 32, 128), (2, 64, 128), (4, 32, 128), (4, 64, 64), (8, 32, 64), (8, 64, 64),
+                 (8, 128, 64), (4, 256, 32), (8, 256, 32)]
+REF_IN_NLC_MS = [(0.78, 0.70), (7.51, 6.05), (12.53, 8.69), (12.35, 8.70), (5.36, 4.63), (5.35, 4.66),
+                 (7.65, 5.98), (12.33, 8.63), (3.76, 3.57), (5.01, 4.25)]
+REF_IN_NC_MS = [(0.77, 0.69), (5.20, 3.85), (10.53, 7.57), (9.27, 6.16), (2.98, 2.17), (3.01, 2.17),
+                (5.32, 3.51), (10.37, 6.38), (1.18, 0.91), (2.57, 1.71)]
+
+
+def run_ref_shapes(dev, peak):
+    """fp16 forward + backward on every shape of the reference's benchmark scripts: device time
+    per step (eager launches through the public API, CUDA events, 20 steps after 10 warm-up
+    steps as the scripts do) next to the published wall-clock figures of the fused TF op."""
+    import torch
+    import atex_b200 as A
+    rows = []
+    g = torch.Generator(device=dev).manual_seed(3)
+
+    def time_steps(fn):
+        for _ in range(10):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(20):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 20
+
+    for shape, a100, h100 in REF_LN_SHAPES:
+        x = torch.randn(shape, generator=g, device=dev, dtype=torch.float32).half()
+        dy = torch.ones_like(x)                       # d(sum y)/dy, as in the script
+        gamma = torch.ones(shape[1], device=dev)
+        beta = torch.zeros(shape[1], device=dev)
+
+        def step():
+            y, m, s = A.fused_layer_norm_op(x, gamma, beta, axis=[1])
+            A.fused_layer_norm_grad_op(dy, x, gamma, m, s, axis=[1])
+        ms = time_steps(step)
+        E = x.numel()
+        rows.append({"op": "LayerNorm", "shape": list(shape), "ms": ms, "gbps": 10 * E / ms / 1e6,
+                     "frac_of_measured": 10 * E / ms / 1e6 / peak, "ref_A100_ms": a100, "ref_H100_ms": h100})
+        del x, dy
+    for fmt, table in (("N...C", REF_IN_NLC_MS), ("NC...", REF_IN_NC_MS)):
+        for (n, c, d), (a100, h100) in zip(REF_IN_SHAPES, table):
+            shape = (n, d, d, d, c) if fmt == "N...C" else (n, c, d, d, d)
+            x = torch.randn(shape, generator=g, device=dev, dtype=torch.float32).half()
+            dy = torch.ones_like(x)
+            gamma, beta = torch.ones(c, device=dev), torch.zeros(c, device=dev)
+
+            def step():
+                y, m, s = A.fused_instance_norm_op(x, gamma, beta, data_format=fmt)
+                A.fused_instance_norm_grad_op(dy, x, gamma, m, s, data_format=fmt)
+            ms = time_steps(step)
+            E = x.numel()
+            rows.append({"op": "InstanceNorm " + fmt, "shape": list(shape), "ms": ms, "gbps": 10 * E / ms / 1e6,
+                         "frac_of_measured": 10 * E / ms / 1e6 / peak, "ref_A100_ms": a100, "ref_H100_ms": h100})
+            del x, dy
+            torch.cuda.empty_cache()
+    return rows
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -507,6 +578,19 @@ def main():
     lib = _lib.load()
     mode = scaling_mode(args, world)
     peak, peak_kind = measured_peak()
+
+    if args.ref_shapes:
+        if rank == 0:
+            rows = run_ref_shapes(dev, peak)
+            print(json.dumps({
+                "metric": "ref_benchmark_shapes_fwd_bwd_ms", "unit": "ms", "n_gpus": 1, "dtype": "f16",
+                "data": "synthetic", "higher_is_better": False,
+                "value": sum(r["ms"] for r in rows),
+                "note": "device time of fwd+bwd through the public API on the shapes of the reference's "
+                        "benchmark scripts; ref_*_ms are the README's wall-clock figures of the fused TF op "
+                        "on A100 / H100 (they include TensorFlow's eager overhead and a reduce_sum)",
+                "shapes": rows}), flush=True)
+        return
 
     w = T.WORKLOADS[args.workload]
     if args.batch:
