@@ -57,6 +57,8 @@ SIGNATURES = {
     "nvn_in_fwd_workspace_bytes": (_sz, [_int, _i64, _i64, _i64, _int]),
     "nvn_in_bwd_workspace_bytes": (_sz, [_int, _i64, _i64, _i64, _int]),
     "nvn_ln_fwd": (_int, [_int, _vp, _vp, _vp, _i64, _i64, _c.c_float, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "nvn_ln_fwd_residual": (_int, [_int, _vp, _vp, _vp, _vp, _i64, _i64, _c.c_float, _vp, _vp, _vp, _vp,
+                                   _vp, _sz, _vp]),
     "nvn_ln_bwd": (_int, [_int, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "nvn_in_fwd": (_int, [_int, _vp, _vp, _vp, _i64, _i64, _i64, _int, _c.c_float, _vp, _vp, _vp,
                           _vp, _sz, _vp]),

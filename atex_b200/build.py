@@ -37,6 +37,7 @@ def _units():
     for t, tname in ((0, "f32"), (1, "f16"), (2, "bf16")):
         for b, dname in ((0, "fwd"), (1, "bwd")):
             units.append((f"rows_{tname}_{dname}.o", "rows_inst.cu", [f"-DNVN_T={t}", f"-DNVN_BWD={b}"]))
+        units.append((f"rows_res_{tname}.o", "rows_res_inst.cu", [f"-DNVN_T={t}"]))
     units.append(("rows_wide.o", "rows_wide.cu", []))
     units.append(("twophase.o", "twophase.cu", []))
     units.append(("colreduce.o", "colreduce.cu", []))
@@ -93,10 +94,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
     units = _units()
     with ThreadPoolExecutor(max_workers=min(len(units), os.cpu_count() or 4)) as ex:
         objs = list(ex.map(compile_one, units))
-    cmd = [nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+    # link beside the target and rename: a reader never sees a half-written library
+    tmp = LIB + ".tmp"
+    cmd = [nvcc, "-shared", "-o", tmp, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, LIB)
     with open(stamp, "w") as f:
         f.write(digest)
     return LIB

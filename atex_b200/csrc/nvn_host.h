@@ -32,6 +32,15 @@ struct RowsArgs {
   int* status;  // device status word: set non-zero when a bounded wait gave up
 };
 
+// Arguments of the residual-add forward (rows_fwd_kernel<..., RES = true>): the row that is
+// normalised is s = T(x + res), which is also written to sum_out.  A type of its own, so
+// that the parameter block - and with it the generated code - of every other instantiation
+// of the row kernels stays what their shapes were tuned with.
+struct RowsResArgs : RowsArgs {
+  const void* res;
+  void* sum_out;
+};
+
 struct RowsPlan {
   int grid;
   int block;
@@ -114,6 +123,9 @@ inline cudaLaunchConfig_t dependent_launch_config(dim3 grid, dim3 block, size_t 
 
 int device_sm_count();
 void count_launch();
+// Whether the row kernels are launched with the programmatic-stream-serialization
+// attribute (their launch then overlaps the predecessor's tail); see variant key `pdl`.
+bool use_dependent_launch();
 
 // Function attributes (the opt-in to more than 48 KB of dynamic shared memory, non-portable
 // cluster sizes) belong to one device's context, and one process may drive several devices
@@ -211,6 +223,22 @@ NVN_DECLARE_ROWS(rows_f16_fwd)
 NVN_DECLARE_ROWS(rows_f16_bwd)
 NVN_DECLARE_ROWS(rows_bf16_fwd)
 NVN_DECLARE_ROWS(rows_bf16_bwd)
+
+// LayerNorm forward fused with the residual add that precedes it in a pre-norm transformer
+// block (rows_res_inst.cu): s = T(x + res) is written to a.sum_out and normalised in the same
+// pass.  Covers rows of up to 4096 128-bit vectors with 128-bit accesses; rows_res_ok says
+// whether a problem qualifies (the C ABI falls back to an add kernel plus the plain forward).
+bool rows_res_ok(int dtype, int64_t D, size_t align, size_t par_align);
+cudaError_t rows_res_launch(int dtype, const RowsResArgs& a, cudaStream_t s);
+cudaError_t rows_res_f32(const RowsResArgs& a, cudaStream_t s);
+cudaError_t rows_res_f16(const RowsResArgs& a, cudaStream_t s);
+cudaError_t rows_res_bf16(const RowsResArgs& a, cudaStream_t s);
+cudaError_t residual_add_f32(const void* x, const void* res, void* out, int64_t count, cudaStream_t s);
+cudaError_t residual_add_f16(const void* x, const void* res, void* out, int64_t count, cudaStream_t s);
+cudaError_t residual_add_bf16(const void* x, const void* res, void* out, int64_t count, cudaStream_t s);
+// The fallback's element-wise s = T(x + res) for any size and alignment.
+cudaError_t residual_add_launch(int dtype, const void* x, const void* res, void* sum_out,
+                                int64_t count, cudaStream_t s);
 
 // Deterministic second stage of the dgamma / dbeta reduction: sums P partial
 // rows of [2][F] floats (dgamma then dbeta) in a fixed order.

@@ -63,12 +63,14 @@ constexpr int64_t kHeldRingMinBytes = 64ll << 20;
 //   wide_fwd=I wide_bwd=I   index into the shape tables of rows_wide.cu (used when the row
 //                           fills that shape)
 //   stream_block=256|512    persistent channels-last kernels: threads per CTA
+//   pdl=0                   launch the row kernels without programmatic stream serialization
 struct Variant {
   int wide = 0;  // 0 default, 1 two-phase, 2 cluster
   int nlc = 0;   // 0 default, 1 two-phase, 2 on-chip but no warp-per-item, 3 persistent
   int fwd_shape = -1, bwd_shape = -1, affine_shape = -1;
   int wide_fwd = -1, wide_bwd = -1;
   int stream_block = 0;  // persistent channels-last kernels: threads per CTA (256 or 512)
+  int pdl = 1;           // programmatic dependent launch of the row kernels
 };
 
 const Variant& variant() {
@@ -95,6 +97,7 @@ const Variant& variant() {
       if (key == "wide_fwd") r.wide_fwd = atoi(val.c_str());
       if (key == "wide_bwd") r.wide_bwd = atoi(val.c_str());
       if (key == "stream_block") r.stream_block = atoi(val.c_str());
+      if (key == "pdl") r.pdl = atoi(val.c_str());
     }
     return r;
   }();
@@ -627,6 +630,8 @@ int device_sm_count() {
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
+bool use_dependent_launch() { return variant().pdl != 0; }
+
 namespace {
 // Raised by a kernel whose bounded wait on an asynchronous copy gave up.
 __device__ int g_status_word = 0;
@@ -647,6 +652,22 @@ int* device_status_word() {
     g_status_ptr[dev] = static_cast<int*>(p);
   }
   return g_status_ptr[dev];
+}
+
+bool rows_res_ok(int dtype, int64_t D, size_t align, size_t par_align) {
+  const int V = full_epv(dtype);
+  return D % V == 0 && D / V <= 4096 && align >= 16 && par_align >= 16;
+}
+
+cudaError_t rows_res_launch(int dtype, const RowsResArgs& a, cudaStream_t s) {
+  return dtype == NVN_F32 ? rows_res_f32(a, s) : (dtype == NVN_F16 ? rows_res_f16(a, s) : rows_res_bf16(a, s));
+}
+
+cudaError_t residual_add_launch(int dtype, const void* x, const void* res, void* sum_out,
+                                int64_t count, cudaStream_t s) {
+  return dtype == NVN_F32 ? residual_add_f32(x, res, sum_out, count, s)
+                          : (dtype == NVN_F16 ? residual_add_f16(x, res, sum_out, count, s)
+                                              : residual_add_bf16(x, res, sum_out, count, s));
 }
 
 }  // namespace nvn
@@ -802,6 +823,43 @@ int nvn_ln_fwd(int dtype, const void* x, const float* gamma, const float* beta, 
   return run_rows(dtype, false, false, nullptr, x, gamma, beta, nullptr, nullptr, N, D, N, 1,
                   epsilon, y, mean, inv_std, nullptr, nullptr, workspace, workspace_bytes,
                   static_cast<cudaStream_t>(stream));
+}
+
+int nvn_ln_fwd_residual(int dtype, const void* x, const void* residual, const float* gamma,
+                        const float* beta, int64_t N, int64_t D, float epsilon, void* sum_out,
+                        void* y, float* mean, float* inv_std, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  if (!valid_dtype(dtype) || N < 0 || D < 0) return NVN_ERR_INVALID_ARGUMENT;
+  if (N == 0 || D == 0) return NVN_OK;
+  if (x == nullptr || residual == nullptr || gamma == nullptr || beta == nullptr ||
+      sum_out == nullptr || y == nullptr || mean == nullptr || inv_std == nullptr)
+    return NVN_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t align = common_alignment({x, residual, sum_out, y});
+  const size_t par_align = common_alignment({gamma, beta});
+  if (rows_res_ok(dtype, D, align, par_align)) {
+    RowsResArgs a = {};
+    a.x = x;
+    a.res = residual;
+    a.sum_out = sum_out;
+    a.gamma = gamma;
+    a.beta = beta;
+    a.out = y;
+    a.mean = mean;
+    a.ivar = inv_std;
+    a.N = N;
+    a.D = D;
+    a.C = 1;
+    a.eps = epsilon;
+    a.status = device_status_word();
+    const cudaError_t e = rows_res_launch(dtype, a, s);
+    return e == cudaSuccess ? NVN_OK : fail_cuda(e);
+  }
+  // any other width or alignment: the sum as a kernel of its own, then the plain forward
+  const cudaError_t e = residual_add_launch(dtype, x, residual, sum_out, N * D, s);
+  if (e != cudaSuccess) return fail_cuda(e);
+  return nvn_ln_fwd(dtype, sum_out, gamma, beta, N, D, epsilon, y, mean, inv_std, workspace,
+                    workspace_bytes, stream);
 }
 
 static int ln_bwd_impl(int dtype, const void* dy, const void* x, const float* gamma,

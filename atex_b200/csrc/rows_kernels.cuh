@@ -224,10 +224,12 @@ __device__ __forceinline__ void ring_give_up(Ring& ring, int* status, int64_t j,
 // ---------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------
+//   RES   (forward only) the row that is normalised is s = T(x + res); s is written to
+//         a.sum_out.  Plain or register-prefetch loads only.
 template <typename T, int EPV, int TPR, int VPT, int CS, int RB, bool PR, int MINB, int PF,
-          bool EXACT, bool ROW_AFFINE>
+          bool EXACT, bool ROW_AFFINE, bool RES = false>
 __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
-    rows_fwd_kernel(const RowsArgs a) {
+    rows_fwd_kernel(const typename std::conditional<RES, RowsResArgs, RowsArgs>::type a) {
   constexpr int BLOCK = RowBlock<TPR, MINB>::kBlock;
   constexpr int RPC = RowBlock<TPR, MINB>::kRowsPerCta;
   constexpr bool TMA = PF >= 2;
@@ -236,6 +238,7 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   constexpr int VSTRIDE = Map::kStride;
   static_assert(CS == 1 || RPC == 1, "cluster kernels own one row per cluster");
   static_assert(!(TMA && CS > 1) || EXACT, "cluster slices need rows that fill the shape");
+  static_assert(!RES || (!TMA && CS == 1 && !ROW_AFFINE), "residual add: LayerNorm, one CTA per row, no ring");
   constexpr bool PARAMS_IN_REGS = !ROW_AFFINE && PR;
   using M = typename MathSel<EPV>::M;
   using E = typename M::E;
@@ -245,8 +248,9 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   // Programmatic dependent launch: the kernel that follows in the stream may be scheduled
   // as CTAs of this one retire, and this one may have been scheduled while its predecessor
   // was still running - nothing that the predecessor may have written (activations,
-  // parameters) is read before griddep_wait() below.
+  // parameters) is read before griddep_wait().
   griddep_launch_dependents();
+  griddep_wait();
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(8) uint64_t ring_bars[STAGES];
   __shared__ ReduceSmem<RB, BLOCK> sm;
@@ -282,7 +286,12 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   // y may alias x (in-place forward), so these are not __restrict__.
   const P* xp = reinterpret_cast<const P*>(a.x) + vec0;
   P* yp = reinterpret_cast<P*>(a.out) + vec0;
-  griddep_wait();
+  const P* rsp = nullptr;
+  P* sop = nullptr;
+  if constexpr (RES) {
+    rsp = reinterpret_cast<const P*>(a.res) + vec0;
+    sop = reinterpret_cast<P*>(a.sum_out) + vec0;
+  }
 
   E g[PARAMS_IN_REGS ? VPT : 1][NE], b[PARAMS_IN_REGS ? VPT : 1][NE];
   if constexpr (PARAMS_IN_REGS) {
@@ -302,6 +311,7 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   const int64_t batch0 = unit * (RPC * RB);  // first row of this CTA's first batch
   const int64_t nb = batch0 < N ? (N - batch0 + stride - 1) / stride : 0;
   RowTile<T, EPV, VPT, RB> tile;
+  RowTile<T, EPV, VPT, RES ? RB : 1> rtile;   // the residual's row batch
   RowRing<T, EPV, VPT, RB, RPC, CS, STAGES, 1> ring;
   const T* const srcs[1] = {static_cast<const T*>(a.x)};
   unsigned roff[RB];
@@ -316,6 +326,8 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
     }
   } else if constexpr (PF == 1) {
     load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, batch0 + group, N, rowvecs, nvalid, tile);
+    if constexpr (RES)
+      load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(rsp, batch0 + group, N, rowvecs, nvalid, rtile);
   }
   for (int64_t j = 0; j < nb; ++j) {
     const int64_t row0 = batch0 + j * stride + group;
@@ -329,6 +341,8 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
         ring.issue(s, srcs, batch0 + (j + STAGES) * stride, N, D, crank);
     } else if constexpr (PF == 0) {
       load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, row0, N, rowvecs, nvalid, tile);
+      if constexpr (RES)
+        load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(rsp, row0, N, rowvecs, nvalid, rtile);
     }
 
     E xv[RB][VPT][NE];
@@ -339,13 +353,28 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
 #pragma unroll
       for (int v = 0; v < VPT; ++v) {
         unpack<T, EPV>(tile.p[r][v], xv[r][v]);
+        if constexpr (RES) {
+          // s = T(x + res): the sum is rounded to the activation type before anything else
+          // uses it, because the backward pass will read the stored s
+          E rv[NE];
+          unpack<T, EPV>(rtile.p[r][v], rv);
+#pragma unroll
+          for (int e = 0; e < NE; ++e) rv[e] = M::add(xv[r][v][e], rv[e]);
+          const P sp = repack<T, EPV>(rv);
+          if (row0 + r * RPC < N && (EXACT || v < nvalid))
+            store_stream<T, EPV>(reinterpret_cast<T*>(sop + (row0 + r * RPC) * rowvecs + v * VSTRIDE), 0, sp);
+          unpack<T, EPV>(sp, xv[r][v]);
+        }
 #pragma unroll
         for (int e = 0; e < NE; ++e) acc = M::add(acc, xv[r][v][e]);
       }
       s_[r] = M::hsum(acc);
     }
-    if constexpr (PF == 1)
+    if constexpr (PF == 1) {
       load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(xp, row0 + stride, N, rowvecs, nvalid, tile);
+      if constexpr (RES)
+        load_tile<T, EPV, VPT, RB, RPC, VSTRIDE, EXACT>(rsp, row0 + stride, N, rowvecs, nvalid, rtile);
+    }
     group_allreduce<RB, TPR, BLOCK, CS>(s_, sm, phase, warp, lane);
 
     float mean[RB], q[RB];
@@ -442,6 +471,7 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   // The column reduction that follows may be scheduled as CTAs of this kernel retire; this
   // kernel itself reads nothing its predecessor may have written before griddep_wait().
   griddep_launch_dependents();
+  griddep_wait();
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(8) uint64_t ring_bars[STAGES];
   __shared__ ReduceSmem<2 * RB, BLOCK> sm;
@@ -476,7 +506,6 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   const P* __restrict__ xp = reinterpret_cast<const P*>(a.x) + vec0;
   const P* __restrict__ dyp = reinterpret_cast<const P*>(a.dy) + vec0;
   P* __restrict__ dxp = reinterpret_cast<P*>(a.out) + vec0;
-  griddep_wait();
 
   E g[PARAMS_IN_REGS ? VPT : 1][NE];
   E dg[ROW_AFFINE ? 1 : VPT][NE], db[ROW_AFFINE ? 1 : VPT][NE];
@@ -907,6 +936,7 @@ inline cudaError_t launch_rows_exact(const RowsArgs& a, cudaStream_t stream, boo
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[0].val.programmaticStreamSerializationAllowed = use_dependent_launch() ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (CS > 1) {

@@ -30,7 +30,7 @@ from . import _lib
 
 __all__ = [
     "InvalidArgumentError",
-    "fused_layer_norm_op", "fused_layer_norm_grad_op",
+    "fused_layer_norm_op", "fused_layer_norm_grad_op", "fused_layer_norm_residual_op",
     "fused_instance_norm_op", "fused_instance_norm_grad_op",
     "_layer_norm_grad", "_instance_norm_grad",
     "LayerNormalization", "InstanceNormalization",
@@ -250,6 +250,45 @@ def fused_layer_norm_op(x, scale, offset, axis: Iterable[int] = (-1,), epsilon: 
                             ws_ptr, ws_bytes, stream)
     _check(st, "nvn_ln_fwd")
     return y, mean, inv_std
+
+
+def fused_layer_norm_residual_op(x, residual, scale, offset, axis: Iterable[int] = (-1,),
+                                 epsilon: float = 0.001, out: torch.Tensor | None = None,
+                                 out_sum: torch.Tensor | None = None, out_stats=None):
+    """Residual add + FusedLayerNorm in one pass: returns (y, s, reserve_space_1,
+    reserve_space_2) with s = (x + residual) rounded to x's dtype and y = LayerNorm(s).
+
+    The step in front of every LayerNorm of a pre-norm transformer block; the gradient op is
+    fused_layer_norm_grad_op on s (its x_backprop is the gradient of x and of residual).
+    `out_sum` may be `x` or `residual` to update the residual stream in place.  The
+    reference has no such op (its layer calls the bare norm, nv_norm_ops.py:85-99)."""
+    _require(isinstance(x, torch.Tensor) and x.dim() > 0, "input must be at least 1-dimensional",
+             x if isinstance(x, torch.Tensor) else "")
+    code = _dtype_code(x, "x")
+    if not isinstance(residual, torch.Tensor) or residual.shape != x.shape or residual.dtype != x.dtype:
+        raise InvalidArgumentError("residual must have the shape and dtype of x")
+    scale, offset = _param(scale, "scale"), _param(offset, "offset")
+    axis = _axis_list(axis)
+    N, D = _ln_dims(x, axis)
+    _require(scale.numel() == D, "scale must have the same number of elements as the features "
+             "of x, got ", scale.numel(), " and ", D)
+    _require(offset.numel() == D, "offset must have the same number of elements as the features "
+             "of x, got ", offset.numel(), " and ", D)
+    x, residual, scale, offset = _on_device((x, "x"), (residual, "residual"), (scale, "scale"),
+                                            (offset, "offset"))
+    y = _like_output(x, out, "out")
+    s = _like_output(x, out_sum, "out_sum")
+    mean, inv_std = _stats_outputs(N, x.device, out_stats)
+    with _device_guard(x.device):
+        lib = _lib.load()
+        stream = _stream(x.device)
+        ws_ptr, ws_bytes = _workspace(x.device, stream, _ws_bytes("nvn_ln_fwd_workspace_bytes", code, N, D))
+        st = lib.nvn_ln_fwd_residual(code, x.data_ptr(), residual.data_ptr(), scale.data_ptr(),
+                                     offset.data_ptr(), N, D, float(epsilon), s.data_ptr(),
+                                     y.data_ptr(), mean.data_ptr(), inv_std.data_ptr(), ws_ptr,
+                                     ws_bytes, stream)
+    _check(st, "nvn_ln_fwd_residual")
+    return y, s, mean, inv_std
 
 
 def _grad_outputs(scale: torch.Tensor, out_grads):

@@ -553,6 +553,30 @@ def run_ref_shapes(dev, peak):
     return rows
 
 
+def measure_residual(dev, peak, steps=20):
+    """Forward of the residual-add LayerNorm on the c2 shape: s = x + r and y = LN(s) in one
+    pass.  Algorithmic bytes: x and r read, s and y written (4 tensor passes)."""
+    import torch
+    import atex_b200 as A
+    from atex_b200 import testing as T
+    w = T.WORKLOADS["c2"]
+    gamma_h, beta_h = T.make_params(w)
+    gamma, beta = gamma_h.to(dev), beta_h.to(dev)
+    x, r = device_inputs(w, dev, 91)
+    y, s_out = torch.empty_like(x), torch.empty_like(x)
+    stats = (torch.empty(w.N, dtype=torch.float32, device=dev), torch.empty(w.N, dtype=torch.float32, device=dev))
+
+    def body(_i):
+        A.fused_layer_norm_residual_op(x, r, gamma, beta, axis=[-1], epsilon=w.eps, out=y, out_sum=s_out,
+                                       out_stats=stats)
+    ms = _graph_ms(torch, body, 1, steps)
+    nbytes = 4 * w.elements * T.ELEM_SIZE[w.dtype] + 2 * w.D * 4 + 2 * w.N * 4
+    del x, r, y, s_out
+    torch.cuda.empty_cache()
+    return {"workload": f"residual add + LayerNorm forward {w.dtype} {list(w.shape())}", "graph_ms": ms,
+            "algorithmic_bytes": nbytes, "gbps": nbytes / ms / 1e6, "frac_of_measured": nbytes / ms / 1e6 / peak}
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -782,6 +806,8 @@ def main():
         if per_config:
             worst_name = min(per_config, key=lambda n: per_config[n]["frac_of_measured"])
             worst = {"config": worst_name, "frac_of_measured": per_config[worst_name]["frac_of_measured"]}
+            if args.configs == "all":
+                per_config["residual_fwd_c2"] = measure_residual(dev, peak)
 
     if rank != 0:
         if world > 1:

@@ -131,6 +131,22 @@ NVN_API int nvn_ln_fwd(int dtype, const void* x, const float* gamma, const float
                        float* inv_std, void* workspace, size_t workspace_bytes,
                        void* stream);
 
+/* LayerNorm forward fused with the residual add that precedes it in a pre-norm block:
+ *   s_ij = T(x_ij + residual_ij)      (the sum in fp32, rounded once to T, written to sum_out)
+ *   y, mean, inv_std = LayerNorm(s)   as in nvn_ln_fwd
+ * The backward pass is nvn_ln_bwd on s: its dx is the gradient of both x and residual.
+ * sum_out may alias x or residual; y may alias any of them.  Workspace: as for nvn_ln_fwd
+ * (nvn_ln_fwd_workspace_bytes).  Rows of up to 4096 128-bit vectors in 16-byte aligned
+ * buffers run as one kernel that reads x and residual once (4 tensor passes); anything else
+ * runs an add kernel followed by nvn_ln_fwd (5 passes), with identical results.
+ * No counterpart in the reference: nv_norms.LayerNormalization calls the bare op
+ * (nv_norm_ops.py:85-99) and the add is a separate TensorFlow kernel. */
+NVN_API int nvn_ln_fwd_residual(int dtype, const void* x, const void* residual,
+                                const float* gamma, const float* beta, int64_t N, int64_t D,
+                                float epsilon, void* sum_out, void* y, float* mean,
+                                float* inv_std, void* workspace, size_t workspace_bytes,
+                                void* stream);
+
 /* dy, x, dx: [N, D] of T.  dgamma, dbeta: [D] fp32.
  *   dgamma_j = sum_i dy_ij (x_ij - mean_i) inv_std_i      dbeta_j = sum_i dy_ij
  *   dx_ij    = dy_ij gamma_j inv_std_i
