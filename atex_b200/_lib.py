@@ -38,7 +38,8 @@ class DpComm(ctypes.Structure):
     """nvn_dp_comm of include/nvnorms.h."""
     _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int),
                 ("recv", ctypes.c_void_p * NVN_DP_MAX_RANKS),
-                ("epoch", ctypes.c_uint32), ("defer", ctypes.c_int)]
+                ("epoch", ctypes.c_uint32), ("defer", ctypes.c_int),
+                ("device_epochs", ctypes.c_void_p)]
 
 
 # name -> (restype, argtypes); mirrors include/nvnorms.h declaration by declaration

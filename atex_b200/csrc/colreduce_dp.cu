@@ -46,7 +46,34 @@ struct DpPtrs {
   int rank, world;
   unsigned epoch;
   int* status;
+  unsigned* ctr;  // device-side epochs (nvn_dp_comm::device_epochs) or nullptr
 };
+
+// Device-side epochs: with nvn_dp_comm::device_epochs set, a kernel takes its epoch from
+// device memory instead of from its arguments, so that a CUDA graph that holds these
+// launches can be replayed (a replay repeats the arguments, and a repeated epoch would match
+// the stale pairs of the previous replay).  Four words: [0] epoch of the last completed
+// push (or fused) kernel, [1] its CTA ticket, [2] epoch of the last completed finish
+// kernel, [3] its ticket.  Every CTA reads the epoch at its start; the last CTA to leave
+// (ticket == grid size - 1) publishes epoch + 1 for the next launch of the same kind, which
+// stream order keeps behind this one.
+__device__ __forceinline__ unsigned epoch_of(const DpPtrs& c, int word) {
+  if (c.ctr == nullptr) return c.epoch;
+  unsigned v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(c.ctr + word) : "memory");
+  return v + 1;
+}
+__device__ __forceinline__ void publish_epoch(const DpPtrs& c, int word, unsigned epoch) {
+  // called by one thread per CTA after the CTA's last use of the epoch
+  if (c.ctr == nullptr) return;
+  __threadfence();
+  const unsigned t = atomicAdd(c.ctr + word + 1, 1u);
+  if (t == gridDim.x - 1) {
+    atomicExch(c.ctr + word + 1, 0u);
+    __threadfence();
+    atomicExch(c.ctr + word, epoch);
+  }
+}
 
 __device__ __forceinline__ void st_pair(uint2* p, float v, unsigned epoch) {
   asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)),
@@ -71,9 +98,11 @@ __global__ void __launch_bounds__(kTX* TY)
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int64_t F2 = 2 * F;
   const int64_t col = (static_cast<int64_t>(blockIdx.x) * kTX + tx) * kW;
-  const int64_t slot = static_cast<int64_t>(c.epoch & 3u) * c.world;
+  if constexpr (PUSH) griddep_wait();  // the partial rows come from the kernel launched just before
+  constexpr int kWord = PUSH ? 0 : 2;
+  const unsigned epoch = epoch_of(c, kWord);
+  const int64_t slot = static_cast<int64_t>(epoch & 3u) * c.world;
   if constexpr (PUSH) {
-  griddep_wait();  // the partial rows come from the kernel launched just before
   float s[kW] = {0.f, 0.f, 0.f, 0.f};
   if (col < F2) {
     for (int64_t p = ty; p < P; p += TY) {
@@ -100,11 +129,15 @@ __global__ void __launch_bounds__(kTX* TY)
     for (int p = 0; p < c.world; ++p) {
       uint2* dst = c.recv[p] + (slot + c.rank) * F2 + col;
 #pragma unroll
-      for (int w = 0; w < kW; ++w) st_pair(dst + w, o[w], c.epoch);
+      for (int w = 0; w < kW; ++w) st_pair(dst + w, o[w], epoch);
     }
   }
   }  // PUSH
-  if constexpr (!FINISH) return;
+  if constexpr (!FINISH) {
+    __syncthreads();
+    if (tx == 0 && ty == 0) publish_epoch(c, kWord, epoch);
+    return;
+  }
   // bounded poll of this rank's own receive rows, then the sum in rank order
   int ok = 1;
   unsigned polls = 0;
@@ -117,7 +150,7 @@ __global__ void __launch_bounds__(kTX* TY)
         uint2 v = ld_pair(src + w);
         // one budget for the whole thread: after the first element that never arrives the
         // rest are read once and not waited for, so a missing peer costs one time-out
-        while (v.y != c.epoch && ok) {
+        while (v.y != epoch && ok) {
           if (++polls > kPollLimit) ok = 0;
           v = ld_pair(src + w);
         }
@@ -137,6 +170,7 @@ __global__ void __launch_bounds__(kTX* TY)
   if (!__syncthreads_and(ok)) {
     if (tx == 0 && ty == 0 && c.status != nullptr) atomicExch(c.status, 1);
   }
+  if (tx == 0 && ty == 0) publish_epoch(c, kWord, epoch);
 }
 
 template <int TY, bool PUSH, bool FINISH>
@@ -162,6 +196,7 @@ DpPtrs make_ptrs(const nvn_dp_comm* comm) {
   c.world = comm->world;
   c.epoch = comm->epoch;
   c.status = device_status_word();
+  c.ctr = static_cast<unsigned*>(comm->device_epochs);
   for (int i = 0; i < NVN_DP_MAX_RANKS; ++i) {
     c.recv[i] = i < comm->world ? static_cast<uint2*>(comm->recv[i]) : nullptr;
   }

@@ -888,7 +888,7 @@ int nvn_ln_bwd(int dtype, const void* dy, const void* x, const float* gamma, con
 // data-parallel variants reject empty problems instead of silently skipping the kernel.
 static int check_comm(const nvn_dp_comm* c, int64_t F) {
   if (c == nullptr || c->world < 1 || c->world > NVN_DP_MAX_RANKS || c->rank < 0 ||
-      c->rank >= c->world || c->epoch == 0 || F % 2 != 0)
+      c->rank >= c->world || (c->epoch == 0 && c->device_epochs == nullptr) || F % 2 != 0)
     return NVN_ERR_INVALID_ARGUMENT;
   for (int i = 0; i < c->world; ++i)
     if (c->recv[i] == nullptr || !aligned(c->recv[i], 16))

@@ -84,12 +84,15 @@ class GradExchange:
     memory is used and the exchange degenerates to a copy through the rank's own buffer.
     """
 
-    def __init__(self, features: int, device: torch.device, group=None, deferred: bool = False):
+    def __init__(self, features: int, device: torch.device, group=None, deferred: bool = False,
+                 device_epochs: bool = False):
         """deferred=True: the backward op only pushes this rank's vector; call finish()
         (typically on a side stream, see bench.py) to wait for the peers and obtain the sums.
         Start the backward op of step e only after finish() of step e - 2 has completed on
         this rank: there are four receive slots (slot_of_epoch), and a finish that lags its
-        push by L steps needs 2L of them.  An instance is bound to one feature count."""
+        push by L steps needs 2L of them.  An instance is bound to one feature count.
+        device_epochs=True: the kernels count the epochs in device memory, which lets the
+        calls be captured in a CUDA graph and replayed (every rank must choose the same)."""
         lib = _lib.load()
         self.deferred = bool(deferred)
         self.features = int(features)
@@ -119,6 +122,8 @@ class GradExchange:
         self._comm.rank = self.rank
         self._comm.world = self.world
         self._comm.defer = 1 if self.deferred else 0
+        self._epochs = torch.zeros(4, dtype=torch.int32, device=self.device) if device_epochs else None
+        self._comm.device_epochs = self._epochs.data_ptr() if device_epochs else None
         for i in range(self.world):
             self._comm.recv[i] = recv_ptrs[i]
 

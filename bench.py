@@ -66,9 +66,11 @@ def parse_args():
     p.add_argument("--batch", type=int, default=0,
                    help="override the global batch extent (rows / batch items); used for small "
                         "profiler captures, not for reported numbers")
-    p.add_argument("--graph", action="store_true",
-                   help="N = 1: report the CUDA-graph replay of the steps as the headline instead of "
-                        "the eager launches")
+    p.add_argument("--launch", default="graph", choices=["graph", "eager"],
+                   help="'graph' (default): the K timed steps are replayed from a CUDA graph, as a "
+                        "training loop at this granularity would run them (the Python host layer "
+                        "costs ~35 us per step, more than a rank's GPU time at 8 GPUs); 'eager': the "
+                        "headline is the eager launch loop.  The other one is reported beside it.")
     p.add_argument("--collective", default="fused-async", choices=["fused-async", "fused", "nccl"],
                    help="N > 1: 'fused' exchanges dgamma|dbeta inside the last backward kernel over "
                         "peer memory; 'fused-async' pushes there and completes the exchange on a "
@@ -635,7 +637,8 @@ def main():
         exchange = None
         deferred = args.collective == "fused-async"
         if world > 1 and args.collective != "nccl" and F % 2 == 0:
-            exchange = sharding.GradExchange(F, dev, deferred=deferred)
+            # device-side epochs: the exchange can be replayed from a CUDA graph
+            exchange = sharding.GradExchange(F, dev, deferred=deferred, device_epochs=True)
         return Runner(w, xh.to(dev), dyh.to(dev), gamma, beta, exchange=exchange, deferred=deferred,
                       nccl=(world > 1 and exchange is None))
 
@@ -704,17 +707,55 @@ def main():
     eager_ms_per_step = ms_per_step
     fwd_ms = statistics.mean(starts[i].elapsed_time(mids[i][0]) for i in sampled)
     bwd_ms = statistics.mean(mids[i][0].elapsed_time(mids[i][1]) for i in sampled)
-    graph_ms = None
-    if args.graph and world == 1:
-        graph_ms = _graph_ms(torch, r.step, r.nsets, K)
+    # ---- the same K steps replayed from a CUDA graph ----
+    def graph_timed(rr, exchange=True):
+        """ms per step (max over ranks) of K steps replayed from a CUDA graph of S steps, or
+        None when the steps cannot be captured (NCCL collective, K without a usable divisor)."""
+        if args.launch != "graph" or (rr.nccl and exchange):
+            return None, 0
+        S = next((d for d in range(min(K, 32), 0, -1) if K % d == 0 and d % rr.nsets == 0), 0)
+        if S == 0:
+            return None, 0
+        cap = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(cap):
+            for i in range(rr.nsets):
+                rr.step(i, exchange=exchange)
+            rr.drain()
+        barrier()
+        rr.pending = 0      # no wait on events recorded outside the capture
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=cap):
+            for i in range(S):
+                rr.step(i, exchange=exchange)
+            if exchange:
+                rr.drain()
+        rr.pending = 0
+        for _ in range(2):
+            graph.replay()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        g0.record()
+        for _ in range(K // S):
+            graph.replay()
+        g1.record()
+        barrier()
+        ms = max_over_ranks(g0.elapsed_time(g1)) / K
+        del graph
+        return ms, S
+
+    graph_ms, S = graph_timed(r)
+    if graph_ms is not None:
         ms_per_step = graph_ms
 
     # ---- N > 1: compute / exchange split, correctness of the exchange, weak sub-record ----
     split = dp_check = weak = None
     if world > 1:
-        local_ms = timed(r, K, exchange=False)   # the same shard without any exchange
-        split = {"step_ms": eager_ms_per_step, "compute_ms": local_ms,
-                 "exchange_ms": eager_ms_per_step - local_ms,
+        # the same shard without any exchange, launched the same way as the headline
+        local_ms, _ = graph_timed(r, exchange=False)
+        if local_ms is None or graph_ms is None:
+            local_ms = timed(r, K, exchange=False)
+        split = {"launch": "graph" if graph_ms is not None else "eager", "step_ms": ms_per_step,
+                 "compute_ms": local_ms, "exchange_ms": ms_per_step - local_ms,
                  "fwd_interval_ms": max_over_ranks(fwd_ms), "bwd_interval_ms": max_over_ranks(bwd_ms),
                  "note": "compute = the same fwd+bwd on this rank's shard with the local column "
                          "reduction only; exchange = what the step costs on top of it"}
@@ -784,7 +825,9 @@ def main():
         for i in range(3):
             rw.step(i)
         rw.drain()
-        wms = timed(rw, K)
+        wms, _ = graph_timed(rw)
+        if wms is None:
+            wms = timed(rw, K)
         weak = {"scaling": "weak", "per_gpu_batch": w.N, "global_batch": w.N * world,
                 "ms_per_step": wms,
                 "value": world * w.algorithmic_bytes() / (wms * 1e-3) / 1e9, "unit": "GB/s"}
@@ -865,8 +908,12 @@ def main():
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
         "gpu_launches": int(launches) * world, "clocks": clocks,
     }
+    line["eager_ms_per_step"] = eager_ms_per_step
     if graph_ms is not None:
-        line["timing"] = "CUDA-graph replay of the steps; eager launch path: %.4f ms/step" % eager_ms_per_step
+        line["timing"] = ("the %d timed steps replayed from a CUDA graph of %d steps; eager launches through the "
+                          "Python layer: %.4f ms/step" % (K, S, eager_ms_per_step))
+    else:
+        line["timing"] = "eager launches through the Python layer"
     if split is not None:
         line["split"] = split
         line["dp_check"] = dp_check["status"]

@@ -210,6 +210,10 @@ typedef struct nvn_dp_comm {
   uint32_t epoch;
   int defer; /* 0: the backward call completes the exchange.  1: it only reduces and pushes;
                 nvn_dp_finish (same comm contents) waits and writes dgamma / dbeta later. */
+  void* device_epochs; /* NULL, or four zero-initialised uint32 in device memory of this rank:
+                the kernels then count the epochs themselves and ignore `epoch`, which makes
+                the calls replayable from a CUDA graph (a replay repeats its arguments; the
+                epochs must not repeat).  Every rank must use the same mode. */
 } nvn_dp_comm;
 
 /* Second half of a deferred exchange (comm->defer was 1 in the backward call of this

@@ -61,6 +61,48 @@ def test_world_one_exchange_equals_the_plain_backward(lib):
     assert lib.nvn_device_status() == _lib.NVN_OK
 
 
+def test_device_side_epochs_let_the_exchange_replay_from_a_cuda_graph(lib):
+    """With nvn_dp_comm::device_epochs the kernels count the epochs themselves: a CUDA graph
+    that holds backward calls with the exchange (whose arguments repeat on every replay) can
+    be replayed any number of times.  world == 1: the rank exchanges with itself through the
+    same kernels, slots and polls."""
+    dev = torch.device("cuda:0")
+    N, D = 1500, 2048
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(N, D, generator=g).bfloat16().to(dev)
+    dy = torch.randn(N, D, generator=g).bfloat16().to(dev)
+    gamma = (torch.rand(D, generator=g) + 0.5).to(dev)
+    y, m, s = A.fused_layer_norm_op(x, gamma, torch.zeros_like(gamma))
+    ref = A.fused_layer_norm_grad_op(dy, x, gamma, m, s)
+    for deferred in (False, True):
+        ex = sharding.GradExchange(D, dev, deferred=deferred, device_epochs=True)
+        dx = torch.empty_like(x)
+        grads = (torch.empty_like(gamma), torch.empty_like(gamma))
+
+        def steps(k):
+            for _ in range(k):
+                A.fused_layer_norm_grad_op(dy, x, gamma, m, s, grad_exchange=ex, out=dx, out_grads=grads)
+                if deferred:
+                    ex.finish(grads[0], grads[1])
+        cap = torch.cuda.Stream()
+        with torch.cuda.stream(cap):
+            steps(2)                      # eager first: epochs 1, 2
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=cap):
+            steps(3)                      # three epochs per replay: slots wrap around
+        for _ in range(5):
+            grads[0].zero_(); grads[1].zero_(); dx.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(dx, ref[0]) and torch.equal(grads[0], ref[1]) and torch.equal(grads[1], ref[2])
+        steps(1)                          # and eager again after the replays
+        torch.cuda.synchronize()
+        assert torch.equal(grads[0], ref[1])
+        assert int(ex._epochs[0].item()) == 2 + 3 * 5 + 1
+    assert lib.nvn_device_status() == _lib.NVN_OK
+
+
 def test_dp_entry_points_validate_their_communicator(lib):
     c = _lib.DpComm()
     c.rank, c.world, c.epoch = 0, 1, 1  # null buffers
