@@ -107,8 +107,16 @@ cudaError_t colreduce_launch(const float* partials, int64_t P, int64_t F, float*
   if (vec) {
     if (P <= 4) return launch<1, 4>(partials, P, F, dgamma, dbeta, s);
     if (P <= 32) return launch<4, 4>(partials, P, F, dgamma, dbeta, s);
-    if (P <= 128 || 2 * F >= 32768) return launch<8, 4>(partials, P, F, dgamma, dbeta, s);
-    return launch<32, 4>(partials, P, F, dgamma, dbeta, s);
+    // Few columns and more than a handful of partial rows (LayerNorm backward at D = 1024: 444
+    // rows of 2048 floats): four columns per thread would leave 16 CTAs to fetch 3.6 MB, a
+    // chain of L2 latencies.  One column per thread gives four times as many CTAs; the row
+    // lanes (TY), hence the order of every column's additions, stay the same.
+    const bool narrow = col_blocks < 64;
+    if (P <= 128 || 2 * F >= 32768)
+      return narrow ? launch<8, 1>(partials, P, F, dgamma, dbeta, s)
+                    : launch<8, 4>(partials, P, F, dgamma, dbeta, s);
+    return narrow ? launch<32, 1>(partials, P, F, dgamma, dbeta, s)
+                  : launch<32, 4>(partials, P, F, dgamma, dbeta, s);
   }
   if (P <= 32) return launch<4, 1>(partials, P, F, dgamma, dbeta, s);
   return launch<32, 1>(partials, P, F, dgamma, dbeta, s);

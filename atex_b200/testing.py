@@ -94,6 +94,21 @@ def scaled(w: Workload, N: int) -> Workload:
                     w.x_kind, w.gamma_kind, w.index)
 
 
+def workload_from_spec(spec: str) -> Workload:
+    """A benchmark configuration by name ("c2"), or a problem of any shape:
+    "ln:N:D:dtype" or "in:N:C:S1xS2x...:dtype:nlc|nc" (dtype f32 | f16 | bf16)."""
+    if spec in WORKLOADS:
+        return WORKLOADS[spec]
+    f = spec.split(":")
+    if f[0] == "ln" and len(f) == 4:
+        return Workload(spec, "ln", f[3], int(f[1]), int(f[2]), eps=1e-5, index=8)
+    if f[0] == "in" and len(f) == 6:
+        sp = tuple(int(v) for v in f[3].split("x"))
+        return Workload(spec, "in", f[4], int(f[1]), math.prod(sp), C=int(f[2]), channel_first=(f[5] == "nc"),
+                        eps=1e-3, spatial=sp, index=9)
+    raise ValueError(f"unknown workload {spec!r}")
+
+
 def _rng(w: Workload, tensor: int, block: int) -> np.random.Generator:
     return np.random.default_rng([1000 * w.index + tensor, block])
 

@@ -45,8 +45,8 @@ if ROOT not in sys.path:
 
 # DRAM traffic (dram__bytes_read + dram__bytes_write) of one launch of the dominant backward
 # kernel, per row / batch item, from ncu captures of reduced batches (traffic grows in
-# proportion to the batch).  c2: 370.9 MB for 16384 rows.
-NCU_BWD_TRAFFIC_BYTES_PER_ENTRY = {"c2": 370.93e6 / 16384}
+# proportion to the batch).  c2: 268.6 MB read + 102.3 MB written for 16384 rows.
+NCU_BWD_TRAFFIC_BYTES_PER_ENTRY = {"c2": (268.6e6 + 102.3e6) / 16384}
 
 NOMINAL_PEAK_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
@@ -58,7 +58,9 @@ def parse_args():
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=50)
     p.add_argument("--warmup", type=int, default=5)
-    p.add_argument("--workload", default="c2")
+    p.add_argument("--workload", default="c2",
+                   help="a benchmark configuration (c1 ... c5) or a shape: ln:N:D:dtype, "
+                        "in:N:C:S1xS2x..:dtype:nlc|nc")
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--scaling", default="auto", choices=["auto", "weak", "strong"],
                    help="N > 1: 'strong' (default) shards the fixed global batch, 'weak' gives every "
@@ -80,6 +82,8 @@ def parse_args():
     p.add_argument("--ref-shapes", action="store_true",
                    help="N = 1: time forward + backward on the shapes of the reference's own benchmark "
                         "scripts (fp16) and print them beside its published A100 / H100 figures")
+    p.add_argument("--residual", action="store_true",
+                   help="N = 1: time only the residual-add LayerNorm forward on the c2 shape (--batch rows)")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     return p.parse_args()
@@ -172,7 +176,7 @@ def run_reference_arm(args, rank, world):
     from atex_b200 import testing as T
     from oracle import oracle
     oracle.build()
-    w = T.WORKLOADS[args.workload]
+    w = T.workload_from_spec(args.workload)
     if args.batch:
         w = T.scaled(w, args.batch)
     mode = scaling_mode(args, world)
@@ -555,13 +559,13 @@ def run_ref_shapes(dev, peak):
     return rows
 
 
-def measure_residual(dev, peak, steps=20):
+def measure_residual(dev, peak, steps=20, rows=0):
     """Forward of the residual-add LayerNorm on the c2 shape: s = x + r and y = LN(s) in one
     pass.  Algorithmic bytes: x and r read, s and y written (4 tensor passes)."""
     import torch
     import atex_b200 as A
     from atex_b200 import testing as T
-    w = T.WORKLOADS["c2"]
+    w = T.WORKLOADS["c2"] if not rows else T.scaled(T.WORKLOADS["c2"], rows)
     gamma_h, beta_h = T.make_params(w)
     gamma, beta = gamma_h.to(dev), beta_h.to(dev)
     x, r = device_inputs(w, dev, 91)
@@ -605,6 +609,13 @@ def main():
     mode = scaling_mode(args, world)
     peak, peak_kind = measured_peak()
 
+    if args.residual:
+        if rank == 0:
+            rec = measure_residual(dev, peak, steps=args.steps, rows=args.batch)
+            print(json.dumps({"metric": "residual_ln_fwd_hbm_gbps", "value": rec["gbps"], "unit": "GB/s",
+                              "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "higher_is_better": True,
+                              "ms_per_step": rec["graph_ms"], "detail": rec}), flush=True)
+        return
     if args.ref_shapes:
         if rank == 0:
             rows = run_ref_shapes(dev, peak)
@@ -618,7 +629,7 @@ def main():
                 "shapes": rows}), flush=True)
         return
 
-    w = T.WORKLOADS[args.workload]
+    w = T.workload_from_spec(args.workload)
     if args.batch:
         w = T.scaled(w, args.batch)
     gamma_h, beta_h = T.make_params(w)

@@ -232,3 +232,18 @@ def test_grad_exchange_is_bound_to_one_feature_count():
     assert ex.epoch == 1
     with pytest.raises(ValueError):
         ex.next_comm(128)
+
+
+def test_workloads_from_shape_specs():
+    w = T.workload_from_spec("c4")
+    assert w is T.WORKLOADS["c4"]
+    w = T.workload_from_spec("ln:12:96:bf16")
+    assert (w.op, w.N, w.D, w.dtype) == ("ln", 12, 96, "bf16") and w.shape() == (12, 96)
+    w = T.workload_from_spec("in:3:16:5x7:f16:nlc")
+    assert w.shape() == (3, 5, 7, 16) and w.D == 35 and not w.channel_first
+    w = T.workload_from_spec("in:3:16:5x7:f32:nc")
+    assert w.shape() == (3, 16, 5, 7) and w.channel_first
+    x, dy = T.make_activations(w)
+    assert x.shape == (3, 16, 5, 7) and x.dtype == torch.float32
+    with pytest.raises(ValueError):
+        T.workload_from_spec("conv:1:2:3")
