@@ -22,7 +22,9 @@ Prints ONE JSON line (rank 0).  Keys beyond the basic contract:
                 `worst_frac` is the smallest fraction of the measured peak among them
   cpu_baseline  the oracle's fp32 port of the reference CPU functors, timed on the host
   e2e           the same metric through the public API with pinned HOST buffers: each step
-                copies x and dy to the device and y, dx, dgamma and dbeta back
+                copies x and dy to the device and y, dx, dgamma and dbeta back; uploads,
+                kernels and downloads run on three streams over two buffer sets, so the
+                copies of neighbouring steps overlap (PCIe is full duplex)
   clocks        nvidia-smi SM clocks and throttle reasons sampled during the timed region
 
 `--impl reference` times the CPU port alone (the reference's own fused op and the Keras /
@@ -320,34 +322,36 @@ class Runner:
         self.push_ev = [torch.cuda.Event() for _ in range(4)]
         self.pending = 0
 
-    def fwd(self, i, x=None):
+    def fwd(self, i, x=None, out=None):
         k = i % self.nsets
         w = self.w
         x = self.xs[k] if x is None else x
+        out = self.ys[k] if out is None else out
         if w.op == "ln":
             return self.A.fused_layer_norm_op(x, self.gamma, self.beta, axis=[-1], epsilon=w.eps,
-                                              out=self.ys[k], out_stats=self.stats[k])
+                                              out=out, out_stats=self.stats[k])
         return self.A.fused_instance_norm_op(x, self.gamma, self.beta, data_format=w.data_format,
-                                             epsilon=w.eps, out=self.ys[k], out_stats=self.stats[k])
+                                             epsilon=w.eps, out=out, out_stats=self.stats[k])
 
-    def bwd(self, i, x=None, dy=None, exchange=True):
+    def bwd(self, i, x=None, dy=None, exchange=True, out=None):
         k = i % self.nsets
         w = self.w
         x = self.xs[k] if x is None else x
         dy = self.dys[k] if dy is None else dy
+        out = self.dxs[k] if out is None else out
         m, s = self.stats[k]
         ex = self.exchange if exchange else None
         if w.op == "ln":
             return self.A.fused_layer_norm_grad_op(dy, x, self.gamma, m, s, axis=[-1],
                                                    out_grads=self.grad_views, grad_exchange=ex,
-                                                   out=self.dxs[k])
+                                                   out=out)
         return self.A.fused_instance_norm_grad_op(dy, x, self.gamma, m, s, data_format=w.data_format,
                                                   out_grads=self.grad_views, grad_exchange=ex,
-                                                  out=self.dxs[k])
+                                                  out=out)
 
-    def step(self, i, ev=None, x=None, dy=None, exchange=True):
+    def step(self, i, ev=None, x=None, dy=None, exchange=True, y_out=None, dx_out=None):
         torch = self.torch
-        self.fwd(i, x)
+        self.fwd(i, x, y_out)
         if ev is not None:
             ev[0].record()
         main = torch.cuda.current_stream()
@@ -355,7 +359,7 @@ class Runner:
         if deferred and self.pending > 1:
             # a push of epoch e needs this rank's finish of e - 2 (four receive slots)
             main.wait_event(self.fin_ev[(self.pending - 2) % 4])
-        self.bwd(i, x, dy, exchange)
+        self.bwd(i, x, dy, exchange, dx_out)
         if ev is not None:
             ev[1].record()
         if deferred:
@@ -720,38 +724,47 @@ def main():
     bwd_ms = statistics.mean(mids[i][0].elapsed_time(mids[i][1]) for i in sampled)
     # ---- the same K steps replayed from a CUDA graph ----
     def graph_timed(rr, exchange=True):
-        """ms per step (max over ranks) of K steps replayed from a CUDA graph of S steps, or
-        None when the steps cannot be captured (NCCL collective, K without a usable divisor)."""
+        """ms per step (max over ranks) of exactly K steps replayed from CUDA graphs - a graph of
+        S steps (a whole number of turns through the buffer sets) replayed K // S times, then a
+        graph of the K % S steps left over - or None when the steps cannot be captured (NCCL
+        collective)."""
         if args.launch != "graph" or (rr.nccl and exchange):
             return None, 0
-        S = next((d for d in range(min(K, 32), 0, -1) if K % d == 0 and d % rr.nsets == 0), 0)
-        if S == 0:
-            return None, 0
+        S = min(K, rr.nsets * max(1, 32 // rr.nsets))
+        reps, rem = divmod(K, S)
         cap = torch.cuda.Stream(device=dev)
         with torch.cuda.stream(cap):
             for i in range(rr.nsets):
                 rr.step(i, exchange=exchange)
             rr.drain()
         barrier()
-        rr.pending = 0      # no wait on events recorded outside the capture
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=cap):
-            for i in range(S):
-                rr.step(i, exchange=exchange)
-            if exchange:
-                rr.drain()
-        rr.pending = 0
+
+        def capture(n):
+            rr.pending = 0      # no wait on events recorded outside the capture
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=cap):
+                for i in range(n):
+                    rr.step(i, exchange=exchange)
+                if exchange:
+                    rr.drain()
+            rr.pending = 0
+            return g
+
+        main = capture(S)
+        tail = capture(rem) if rem else None
         for _ in range(2):
-            graph.replay()
+            main.replay()
         g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         g0.record()
-        for _ in range(K // S):
-            graph.replay()
+        for _ in range(reps):
+            main.replay()
+        if tail is not None:
+            tail.replay()
         g1.record()
         barrier()
         ms = max_over_ranks(g0.elapsed_time(g1)) / K
-        del graph
+        del main, tail
         return ms, S
 
     graph_ms, S = graph_timed(r)
@@ -792,30 +805,61 @@ def main():
                     "bit_identical_on_all_ranks": identical}
 
     # ---- e2e: pinned host buffers in; y, dx and the parameter gradients out, every step ----
+    # Three streams and two buffer sets: the upload of step i + 1 and the download of step
+    # i - 1 run beside the kernels of step i (PCIe is full duplex), as an input pipeline
+    # would; every step still brings all its inputs in and takes all its results out inside
+    # the timed region.
     e2e = None
     if not args.no_e2e:
-        xd, dyd = torch.empty_like(r.xs[0]), torch.empty_like(r.dys[0])
-        y_h = torch.empty_like(x_h).pin_memory()
-        dx_h = torch.empty_like(x_h).pin_memory()
-        out_h = torch.empty(2 * F, dtype=torch.float32).pin_memory()
+        y_h = [torch.empty_like(x_h).pin_memory() for _ in range(2)]
+        dx_h = [torch.empty_like(x_h).pin_memory() for _ in range(2)]
+        out_h = [torch.empty(2 * F, dtype=torch.float32).pin_memory() for _ in range(2)]
+        if r.nsets >= 2:
+            xin, dyin = r.xs, r.dys
+        else:   # one set only: a second pair of device input buffers for the pipeline
+            xin = [r.xs[0], torch.empty_like(r.xs[0])]
+            dyin = [r.dys[0], torch.empty_like(r.dys[0])]
+        yout = [torch.empty_like(r.xs[0]) for _ in range(2)]
+        dxout = [torch.empty_like(r.xs[0]) for _ in range(2)]
+        up, down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        cur = torch.cuda.current_stream(dev)
+        ev_up = [torch.cuda.Event() for _ in range(2)]
+        ev_comp = [torch.cuda.Event() for _ in range(2)]
+        ev_down = [torch.cuda.Event() for _ in range(2)]
 
         def e2e_step(i):
-            xd.copy_(x_h, non_blocking=True)
-            dyd.copy_(dy_h, non_blocking=True)
-            r.step(0, x=xd, dy=dyd)
+            k = i % 2
+            with torch.cuda.stream(up):
+                up.wait_event(ev_comp[k])       # step i - 2 has read these inputs
+                xin[k].copy_(x_h, non_blocking=True)
+                dyin[k].copy_(dy_h, non_blocking=True)
+                ev_up[k].record(up)
+            cur.wait_event(ev_up[k])
+            cur.wait_event(ev_down[k])          # the results of step i - 2 have left
+            r.step(0, x=xin[k], dy=dyin[k], y_out=yout[k], dx_out=dxout[k])
             r.drain()
-            y_h.copy_(r.ys[0], non_blocking=True)
-            dx_h.copy_(r.dxs[0], non_blocking=True)
-            out_h.copy_(r.grad_buf, non_blocking=True)
+            out_h[k].copy_(r.grad_buf, non_blocking=True)
+            ev_comp[k].record(cur)
+            with torch.cuda.stream(down):
+                down.wait_event(ev_comp[k])
+                y_h[k].copy_(yout[k], non_blocking=True)
+                dx_h[k].copy_(dxout[k], non_blocking=True)
+                ev_down[k].record(down)
 
-        Ke = max(3, min(K, 20))
-        for i in range(3):
+        def e2e_join():
+            for k in range(2):
+                cur.wait_event(ev_down[k])
+
+        Ke = max(4, min(K, 20))
+        for i in range(4):
             e2e_step(i)
+        e2e_join()
         s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         s0.record()
         for i in range(Ke):
             e2e_step(i)
+        e2e_join()
         s1.record()
         barrier()
         e2e_ms = max_over_ranks(s0.elapsed_time(s1)) / Ke
@@ -825,7 +869,10 @@ def main():
                "h2d_bytes_per_step": 2 * wl.elements * esz,
                "d2h_bytes_per_step": 2 * wl.elements * esz + 2 * F * 4,
                "ms_per_step": e2e_ms, "steps": Ke,
-               "copies": "per rank and step: x, dy host->device; y, dx, dgamma|dbeta device->host (pinned)"}
+               "copies": "per rank and step: x, dy host->device; y, dx, dgamma|dbeta device->host (pinned); "
+                         "uploads, kernels and downloads on three streams over two buffer sets, so the "
+                         "copies of neighbouring steps overlap"}
+        del yout, dxout
 
     # ---- N > 1: the weak-scaling arrangement (every rank a full batch) as a sub-record ----
     if world > 1 and mode == "strong" and args.scaling == "auto":
@@ -921,8 +968,9 @@ def main():
     }
     line["eager_ms_per_step"] = eager_ms_per_step
     if graph_ms is not None:
-        line["timing"] = ("the %d timed steps replayed from a CUDA graph of %d steps; eager launches through the "
-                          "Python layer: %.4f ms/step" % (K, S, eager_ms_per_step))
+        line["timing"] = ("the %d timed steps replayed from a CUDA graph of %d steps (%d replays, then a graph "
+                          "of the %d steps left over); eager launches through the Python layer: %.4f ms/step"
+                          % (K, S, K // S, K % S, eager_ms_per_step))
     else:
         line["timing"] = "eager launches through the Python layer"
     if split is not None:

@@ -3,7 +3,9 @@ grid barrier per item, item tails kept in shared memory) on shapes far smaller t
 134 MB items they are meant for, so that every corner runs in seconds: items whose vector
 count does not fill the last sweep, fewer sweeps than CTAs (some CTAs idle), a single
 item, several items (ring hand-over from one item to the next), every dtype, C from one
-to sixteen channel vectors.
+to sixteen channel vectors; and two shapes with items of ~43 MB, the smallest size at which a
+part of the item lies outside every CTA's ring after the first phase, so that the second phase
+fetches chunks again on its backward walk.
 
 The dispatcher only sends items of at least 32 MB there; NVN_FORCE_VARIANT=nlc=stream (read
 when the library is loaded) lifts the size rule, so the checks run in a child process.
@@ -33,6 +35,8 @@ cases = [  # N, C, spatial, dtype
     (4, 128, (50, 31), "f16"),         # 16 channel vectors, C = 128
     (1, 32, (7, 3), "f16"),            # 21 voxels: almost every CTA is idle
     (5, 32, (128, 128), "f32"),        # several items back to back
+    (2, 32, (101, 103, 64), "f16"),    # 42.6 MB items: more chunks per CTA than ring stages
+    (3, 16, (150, 150, 30), "f32"),    # 43.2 MB items, fp32, odd item count
 ]
 for i, (N, C, sp, dt) in enumerate(cases):
     code = {"f32": 0, "f16": 1, "bf16": 2}[dt]
@@ -50,14 +54,20 @@ for i, (N, C, sp, dt) in enumerate(cases):
     y2, m2, s2 = A.fused_instance_norm_op(xd, gd, bd, data_format="N...C")
     torch.cuda.synchronize()
     assert torch.equal(y1, y2) and torch.equal(m1, m2) and torch.equal(s1, s2)
+    dyd = dy.cuda()
+    dx1, dg1, db1 = A.fused_instance_norm_grad_op(dyd, xd, gd, m1, s1, data_format="N...C")
+    dx2, dg2, db2 = A.fused_instance_norm_grad_op(dyd, xd, gd, m1, s1, data_format="N...C")
+    torch.cuda.synchronize()
+    assert torch.equal(dx1, dx2) and torch.equal(dg1, dg2) and torch.equal(db1, db2)
 assert lib.nvn_device_status() == 0
 print("stream ok")
 """
 
 
-def test_persistent_channels_last_kernels_on_small_and_ragged_items(tmp_path):
+@pytest.mark.parametrize("variant", ["nlc=stream", "nlc=stream,stream_block=256"])
+def test_persistent_channels_last_kernels_on_small_and_ragged_items(tmp_path, variant):
     script = tmp_path / "stream_worker.py"
     script.write_text(_WORKER)
-    env = dict(os.environ, NVN_ROOT=ROOT, NVN_FORCE_VARIANT="nlc=stream")
+    env = dict(os.environ, NVN_ROOT=ROOT, NVN_FORCE_VARIANT=variant)
     r = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "stream ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
