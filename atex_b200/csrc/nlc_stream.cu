@@ -25,7 +25,12 @@
 //   * phase 2 walks the chunks BACKWARDS: first the chunks still in shared memory, then
 //     the ones read most recently, which L2 still holds in part; outputs are written
 //     with streaming stores so that they displace as little of that as possible;
-//   * while phase 2 drains, the freed slots already load the next item.
+//   * while phase 2 drains, the freed slots already load the next item;
+//   * for items of a few MB the barrier and the merge behind it (~7 us in which a CTA
+//     moves nothing) would cost more than the streaming: the grid then splits into GROUPS
+//     of CTAs (CTA i belongs to group i % groups), each with its own barrier and its own
+//     items (n = group, group + groups, ...), so that one group streams while another
+//     one waits; such items stay in shared memory as a whole or nearly so.
 //
 // All merges have a fixed order (lanes by butterfly, warps and CTAs by index), so results
 // are bit-identical run to run.  No multicast copy; every copy reads this GPU's memory.
@@ -48,6 +53,9 @@ constexpr int kVPC = 4;      // 128-bit vectors per consumer thread and chunk (a
 constexpr int kStages = 6;   // ring stages of BLOCK * kVPC * 16 bytes
 constexpr int kMaxC = 128;   // bounds the per-channel arrays in shared memory
 constexpr unsigned kGridPollLimit = 1u << 24;
+constexpr int kMaxGroups = 8;
+constexpr int kCounterStride = 32;   // unsigneds between two groups' barrier counters (128 bytes)
+constexpr size_t kHeaderBytes = kMaxGroups * kCounterStride * sizeof(unsigned);
 constexpr int kMergeBatch = 8;  // per-CTA partials fetched together when the item's totals are formed
 
 struct StreamArgs {
@@ -62,7 +70,8 @@ struct StreamArgs {
   float* ivar;
   float* part;      // [2][grid][3][C] per-CTA partials, double-buffered by item parity
   float* colpart;   // backward: [N][2][C] per-item (dgamma, dbeta) contributions
-  unsigned* counter;  // grid barrier, zero at launch
+  unsigned* counter;  // one barrier counter per group, kCounterStride apart, zero at launch
+  int groups;         // CTA groups; gridDim.x is a multiple
   int64_t N, C, D;
   float eps;
   int* status;
@@ -128,7 +137,11 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
   const int64_t C = a.C, D = a.D, N = a.N;
   const int CV = static_cast<int>(C / EPV);   // channel vectors per voxel; a power of two <= 32
   const int cv = tid % CV;
-  const int G = gridDim.x, b = blockIdx.x;
+  // this CTA's group: G CTAs, of which it is number b, working on items grp, grp + groups, ...
+  const int groups = a.groups, grp = blockIdx.x % groups;
+  const int G = gridDim.x / groups, b = blockIdx.x / groups;
+  unsigned* const counter = a.counter + grp * kCounterStride;
+  float* const part = a.part + static_cast<int64_t>(grp) * 2 * G * 3 * C;
   // The item in chunks of VPT * BLOCK vectors (one ring stage); CTA b takes chunks b, b + G,
   // b + 2G, ...: at any moment the CTAs read one contiguous window of the item.
   const int64_t item_vecs = D * CV;
@@ -170,12 +183,12 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
   // for the chunk that will occupy the same stage kStages steps later; a step first waits
   // until at most kStages - 1 groups are pending, i.e. until its own chunk has landed.
   for (int c = 0; c < kStages; ++c) {
-    if (c < NCi && N > 0) issue(0, first_v0 + c * stride, c);
+    if (c < NCi && grp < N) issue(grp, first_v0 + c * stride, c);
     cp_async_commit();
   }
 
-  unsigned barriers = 0;
-  for (int64_t n = 0; n < N; ++n) {
+  unsigned barriers = 0;   // also the number of this group's items so far
+  for (int64_t n = grp; n < N; n += groups) {
     // ------------------------------------------------------------------ phase 1
     E acc0[NE], acc1[NE];   // forward: running mean, M2; backward: sum dy, sum dy * (x - mean)
     float cnt = 0.f;
@@ -191,7 +204,7 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
     }
     // the first chunks of this item were started during the last steps of the previous
     // phase 2, in an order that the group count does not cover: wait for all of them once
-    if (n > 0) cp_async_wait<0>();
+    if (barriers > 0) cp_async_wait<0>();
     {
     int stage = 0;
     int64_t v0 = first_v0;
@@ -316,7 +329,7 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
         }
       }
       __syncthreads();
-      float* mine = a.part + ((n & 1) * G + b) * 3 * C;
+      float* mine = part + ((barriers & 1) * G + b) * 3 * C;
       if (tid < C) {
         float m = wpart[0][0][tid], s = wpart[1][0][tid], k = wpart[2][0][tid];
         if constexpr (BWD) {
@@ -348,13 +361,14 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
     }
     // ------------------------------------------------------------ grid barrier
     __syncthreads();
+    const unsigned parity = barriers & 1u;   // of this item's partials
     ++barriers;
     if (tid == 0) {
-      atomicAdd(a.counter, 1u);
+      atomicAdd(counter, 1u);
       const unsigned target = barriers * static_cast<unsigned>(G);
       unsigned polls = 0;
       bool gave_up = false;
-      while (!gave_up && ld_acquire(a.counter) < target) {
+      while (!gave_up && ld_acquire(counter) < target) {
         if (++polls > kGridPollLimit) {
           gave_up = true;
           if (a.status != nullptr) atomicExch(a.status, 2);
@@ -367,7 +381,7 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
     {
       const int SL = BLOCK / static_cast<int>(C);   // threads per channel (C <= 128: >= 2)
       const int c = tid % static_cast<int>(C), slice = tid / static_cast<int>(C);
-      const float* all = a.part + (n & 1) * G * 3 * C;
+      const float* all = part + parity * G * 3 * C;
       // Forward: the (mean, M2, n) partials are restated as sums about CTA 0's mean K of
       // the channel, so that slices and CTAs combine by plain additions in a fixed order.
       float m = 0.f, s = 0.f, k = 0.f;
@@ -484,8 +498,8 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
       // the slots are free: the next chunk of the backward walk, or the next item's phase 1
       if (r + kStages < NCi) {
         issue(n, v0 - kStages * stride, stage);
-      } else if (n + 1 < N && stage < NCi) {
-        issue(n + 1, first_v0 + stage * stride, stage);
+      } else if (n + groups < N && stage < NCi) {
+        issue(n + groups, first_v0 + stage * stride, stage);
       }
       cp_async_commit();
       v0 -= stride;
@@ -515,7 +529,7 @@ constexpr int kMaxCtasPerSm = 2;
 
 size_t nlc_stream_workspace_bytes(bool bwd, int64_t N, int64_t C) {
   const size_t ctas = static_cast<size_t>(device_sm_count()) * kMaxCtasPerSm;
-  size_t b = 256;                                   // the barrier counter
+  size_t b = kHeaderBytes;                          // the barrier counters
   b += (2 * ctas * 3 * C * 4 + 255) / 256 * 256;    // per-CTA partials, two item parities
   if (bwd) b += (static_cast<size_t>(N) * 2 * C * 4 + 255) / 256 * 256;
   return b;
@@ -540,10 +554,11 @@ static cudaError_t stream_launch_b(StreamArgs& a, cudaStream_t s) {
     if (per_sm > kMaxCtasPerSm) per_sm = kMaxCtasPerSm;
     cached_per_sm.store(per_sm, std::memory_order_relaxed);
   }
-  e = cudaMemsetAsync(a.counter, 0, sizeof(unsigned), s);
+  e = cudaMemsetAsync(a.counter, 0, kHeaderBytes, s);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(device_sm_count() * per_sm), 1, 1);
+  const int ctas = device_sm_count() * per_sm / a.groups * a.groups;
+  cfg.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
   cfg.blockDim = dim3(BLOCK, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
@@ -569,8 +584,10 @@ cudaError_t nlc_stream_launch(int dtype, bool bwd, const void* dy, const void* x
                               const float* gamma, const float* beta, const float* mean_in,
                               const float* ivar_in, int64_t N, int64_t C, int64_t D, float eps,
                               void* out, float* mean, float* ivar, void* ws, float* colpart,
-                              int* status, int block, cudaStream_t s) {
+                              int* status, int block, int groups, cudaStream_t s) {
   StreamArgs a = {};
+  a.groups = groups < 1 ? 1 : (groups > kMaxGroups ? kMaxGroups : groups);
+  if (a.groups > N) a.groups = static_cast<int>(N > 0 ? N : 1);
   a.x = x;
   a.dy = dy;
   a.gamma = gamma;
@@ -581,7 +598,7 @@ cudaError_t nlc_stream_launch(int dtype, bool bwd, const void* dy, const void* x
   a.mean = mean;
   a.ivar = ivar;
   a.counter = static_cast<unsigned*>(ws);
-  a.part = reinterpret_cast<float*>(static_cast<char*>(ws) + 256);
+  a.part = reinterpret_cast<float*>(static_cast<char*>(ws) + kHeaderBytes);
   a.colpart = colpart;
   a.N = N;
   a.C = C;

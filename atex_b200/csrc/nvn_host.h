@@ -87,14 +87,15 @@ cudaError_t nlc_onchip_launch(int dtype, bool bwd, const void* dy, const void* x
 // power-of-two number (<= 32) of channel vectors, C <= 128, items of at least 32 MB
 // (`any_size` drops the size rule: tests).  `ws` holds nlc_stream_workspace_bytes; the
 // backward launch leaves colpart[N][2][C].  `block`: 512 threads (one CTA per SM) or 256
-// (two per SM).
+// (two per SM).  `groups`: CTA groups that work on different items at the same time (1 to 8,
+// clamped to N).
 bool nlc_stream_ok(int dtype, int64_t N, int64_t C, int64_t D, bool any_size);
 size_t nlc_stream_workspace_bytes(bool bwd, int64_t N, int64_t C);
 cudaError_t nlc_stream_launch(int dtype, bool bwd, const void* dy, const void* x,
                               const float* gamma, const float* beta, const float* mean_in,
                               const float* ivar_in, int64_t N, int64_t C, int64_t D, float eps,
                               void* out, float* mean, float* ivar, void* ws, float* colpart,
-                              int* status, int block, cudaStream_t s);
+                              int* status, int block, int groups, cudaStream_t s);
 
 // Warp-per-item channels-last InstanceNorm for small items (nlc_small.cu): any dtype, C and
 // alignment, C <= 32 and D * C <= 4096 elements.  Backward leaves colpart[N][2][C].

@@ -63,6 +63,7 @@ constexpr int64_t kHeldRingMinBytes = 64ll << 20;
 //   wide_fwd=I wide_bwd=I   index into the shape tables of rows_wide.cu (used when the row
 //                           fills that shape)
 //   stream_block=256|512    persistent channels-last kernels: threads per CTA
+//   stream_groups=K         persistent channels-last kernels: CTA groups (1 to 8)
 //   pdl=0                   launch the row kernels without programmatic stream serialization
 struct Variant {
   int wide = 0;  // 0 default, 1 two-phase, 2 cluster
@@ -70,6 +71,7 @@ struct Variant {
   int fwd_shape = -1, bwd_shape = -1, affine_shape = -1;
   int wide_fwd = -1, wide_bwd = -1;
   int stream_block = 0;  // persistent channels-last kernels: threads per CTA (256 or 512)
+  int stream_groups = 0; // persistent channels-last kernels: CTA groups (0: by item size)
   int pdl = 1;           // programmatic dependent launch of the row kernels
 };
 
@@ -97,6 +99,7 @@ const Variant& variant() {
       if (key == "wide_fwd") r.wide_fwd = atoi(val.c_str());
       if (key == "wide_bwd") r.wide_bwd = atoi(val.c_str());
       if (key == "stream_block") r.stream_block = atoi(val.c_str());
+      if (key == "stream_groups") r.stream_groups = atoi(val.c_str());
       if (key == "pdl") r.pdl = atoi(val.c_str());
     }
     return r;
@@ -443,6 +446,17 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
 // ---------------------------------------------------------------------------
 constexpr int kStreamBlock = 512;  // threads per CTA of the persistent channels-last kernels
 
+// CTA groups of the persistent kernels: one for items that keep every SM busy for tens of
+// microseconds; smaller items share the GPU, so that one group's barrier and merge hide
+// under another group's streaming.
+int stream_groups(int dtype, int64_t N, int64_t C, int64_t D) {
+  if (variant().stream_groups > 0) return variant().stream_groups;
+  const size_t item_bytes = static_cast<size_t>(D) * C * (dtype == 0 ? 4 : 2);
+  int g = 1;
+  while (g < 8 && (item_bytes * g) < (size_t(32) << 20) && 2 * g <= N) g *= 2;
+  return g;
+}
+
 struct NlcPlan {
   bool stream;  // persistent kernel: one cooperative launch, item tails kept on chip
   bool scalar;
@@ -543,7 +557,8 @@ int run_nlc(int dtype, bool bwd, const void* dy, const void* x, const float* gam
     float* colpart = bwd ? reinterpret_cast<float*>(wsb + p.off_colpart) : nullptr;
     cudaError_t e = nlc_stream_launch(dtype, bwd, dy, x, gamma, beta, mean_in, ivar_in, N, C, D,
                                       eps, out, mean, ivar, wsb, colpart, device_status_word(),
-                                      variant().stream_block > 0 ? variant().stream_block : kStreamBlock, stream);
+                                      variant().stream_block > 0 ? variant().stream_block : kStreamBlock,
+                                      stream_groups(dtype, N, C, D), stream);
     if (e != cudaSuccess) return fail_cuda(e);
     if (bwd) {
       e = comm != nullptr ? colreduce_allreduce_launch(colpart, N, C, comm, dgamma, dbeta, stream)
@@ -992,9 +1007,10 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
     int st = plan_nlc(dtype, bwd, N, C, D, true, &p);
     if (st != NVN_OK) return st;
     if (p.stream) {
-      snprintf(out, out_bytes, "nlc persistent epv=%d consumers=%d ring=6x%dKB",
+      snprintf(out, out_bytes, "nlc persistent epv=%d consumers=%d ring=6x%dKB groups=%d",
                full_epv(dtype), variant().stream_block == 256 ? 256 : kStreamBlock,
-               (variant().stream_block == 256 ? 256 : kStreamBlock) / 16);
+               (variant().stream_block == 256 ? 256 : kStreamBlock) / 16,
+               static_cast<int>(std::min<int64_t>(stream_groups(dtype, N, C, D), N)));
       return NVN_OK;
     }
     if (p.small) {

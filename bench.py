@@ -437,7 +437,7 @@ def measure_config(name, dev, peak, steps=20, host_calls=0):
     import torch
     from atex_b200 import _lib
     from atex_b200 import testing as T
-    w = T.WORKLOADS[name]
+    w = T.workload_from_spec(name)
     gamma_h, beta_h = T.make_params(w)
     gamma, beta = gamma_h.to(dev), beta_h.to(dev)
     x, dy = device_inputs(w, dev, 77 + w.index)
