@@ -513,16 +513,11 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
 
 }  // namespace
 
-bool nlc_stream_ok(int dtype, int64_t N, int64_t C, int64_t D, bool any_size) {
+bool nlc_stream_ok(int dtype, int64_t N, int64_t C, int64_t D) {
   const int epv = dtype == 0 ? 4 : 8;
-  const size_t es = dtype == 0 ? 4 : 2;
-  if (C % epv != 0 || C > kMaxC) return false;
+  if (N < 1 || C % epv != 0 || C > kMaxC) return false;
   const int64_t cv = C / epv;
-  if (cv > 32 || (cv & (cv - 1)) != 0) return false;
-  // items large enough that a grid barrier per item costs little, and every CTA gets at
-  // least a full ring of chunks
-  const size_t item_bytes = static_cast<size_t>(D) * C * es;
-  return N >= 1 && (any_size || item_bytes >= (32u << 20));
+  return cv <= 32 && (cv & (cv - 1)) == 0;
 }
 
 constexpr int kMaxCtasPerSm = 2;

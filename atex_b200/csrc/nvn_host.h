@@ -84,12 +84,12 @@ cudaError_t nlc_onchip_launch(int dtype, bool bwd, const void* dy, const void* x
 // Persistent channels-last InstanceNorm for items far larger than shared memory
 // (nlc_stream.cu): one cooperative launch per direction, the tail of every item stays on
 // chip between the statistics and the normalisation.  nlc_stream_ok: 128-bit accesses, a
-// power-of-two number (<= 32) of channel vectors, C <= 128, items of at least 32 MB
-// (`any_size` drops the size rule: tests).  `ws` holds nlc_stream_workspace_bytes; the
-// backward launch leaves colpart[N][2][C].  `block`: 512 threads (one CTA per SM) or 256
-// (two per SM).  `groups`: CTA groups that work on different items at the same time (1 to 8,
-// clamped to N).
-bool nlc_stream_ok(int dtype, int64_t N, int64_t C, int64_t D, bool any_size);
+// power-of-two number (<= 32) of channel vectors, C <= 128 (whether the items are large
+// enough to be worth it is the dispatcher's decision).  `ws` holds
+// nlc_stream_workspace_bytes; the backward launch leaves colpart[N][2][C].  `block`: 512
+// threads (one CTA per SM) or 256 (two per SM).  `groups`: CTA groups that work on
+// different items at the same time (1 to 8, clamped to N).
+bool nlc_stream_ok(int dtype, int64_t N, int64_t C, int64_t D);
 size_t nlc_stream_workspace_bytes(bool bwd, int64_t N, int64_t C);
 cudaError_t nlc_stream_launch(int dtype, bool bwd, const void* dy, const void* x,
                               const float* gamma, const float* beta, const float* mean_in,

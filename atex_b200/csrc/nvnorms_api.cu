@@ -446,15 +446,25 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
 // ---------------------------------------------------------------------------
 constexpr int kStreamBlock = 512;  // threads per CTA of the persistent channels-last kernels
 
-// CTA groups of the persistent kernels: one for items that keep every SM busy for tens of
-// microseconds; smaller items share the GPU, so that one group's barrier and merge hide
-// under another group's streaming.
-int stream_groups(int dtype, int64_t N, int64_t C, int64_t D) {
-  if (variant().stream_groups > 0) return variant().stream_groups;
-  const size_t item_bytes = static_cast<size_t>(D) * C * (dtype == 0 ? 4 : 2);
+// CTA groups of the persistent kernels, or 0 when the two-phase kernels are the better
+// choice.  One group for items that keep every SM busy for tens of microseconds; smaller
+// items share the GPU, so that one group's barrier and merge hide under another group's
+// streaming: about 64 MB in flight forward, 32 MB backward (whose first phase reads twice
+// as much per item), in powers of two, at most one group per item.  Measured on B200,
+// fp16, C = 32: 8 items of 16.8 MB, two-phase 217 us, persistent with 1 / 2 / 4 / 8 groups
+// 229 / 170 / 166 / 176 us; 16 items of 7 MB, 183 us against 310 / 197 / 152 / 141 us.
+int stream_groups(int dtype, bool bwd, int64_t N, int64_t C, int64_t D) {
+  const double item_bytes = static_cast<double>(D) * C * (dtype == 0 ? 4 : 2);
   int g = 1;
-  while (g < 8 && (item_bytes * g) < (size_t(32) << 20) && 2 * g <= N) g *= 2;
-  return g;
+  if (variant().stream_groups > 0) {
+    g = variant().stream_groups;
+  } else {
+    const double want = (bwd ? 32.0 : 64.0) * 1048576.0 / item_bytes;
+    while (g < 8 && want > g * 1.4142) g *= 2;   // the nearest power of two
+  }
+  if (g > N) g = static_cast<int>(N);
+  if (variant().nlc == 3) return g;
+  return (item_bytes >= 32.0 * 1048576.0 || g * item_bytes >= 24.0 * 1048576.0) ? g : 0;
 }
 
 struct NlcPlan {
@@ -474,8 +484,8 @@ int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, 
   p->scalar = !(vec_ok && C % V == 0);
   // Small items: a warp per item beats a CTA per item below 2048 elements, and is the only
   // one-launch path for channel counts or alignments the vector kernels cannot take.
-  if (vec_ok && allow_onchip && variant().nlc != 1 &&
-      nlc_stream_ok(dtype, N, C, D, variant().nlc == 3)) {
+  if (vec_ok && allow_onchip && variant().nlc != 1 && nlc_stream_ok(dtype, N, C, D) &&
+      stream_groups(dtype, bwd, N, C, D) > 0) {
     p->stream = true;
     size_t off = nlc_stream_workspace_bytes(bwd, N, C);
     if (bwd) {
@@ -558,7 +568,7 @@ int run_nlc(int dtype, bool bwd, const void* dy, const void* x, const float* gam
     cudaError_t e = nlc_stream_launch(dtype, bwd, dy, x, gamma, beta, mean_in, ivar_in, N, C, D,
                                       eps, out, mean, ivar, wsb, colpart, device_status_word(),
                                       variant().stream_block > 0 ? variant().stream_block : kStreamBlock,
-                                      stream_groups(dtype, N, C, D), stream);
+                                      stream_groups(dtype, bwd, N, C, D), stream);
     if (e != cudaSuccess) return fail_cuda(e);
     if (bwd) {
       e = comm != nullptr ? colreduce_allreduce_launch(colpart, N, C, comm, dgamma, dbeta, stream)
@@ -1010,7 +1020,7 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
       snprintf(out, out_bytes, "nlc persistent epv=%d consumers=%d ring=6x%dKB groups=%d",
                full_epv(dtype), variant().stream_block == 256 ? 256 : kStreamBlock,
                (variant().stream_block == 256 ? 256 : kStreamBlock) / 16,
-               static_cast<int>(std::min<int64_t>(stream_groups(dtype, N, C, D), N)));
+               stream_groups(dtype, bwd, N, C, D));
       return NVN_OK;
     }
     if (p.small) {

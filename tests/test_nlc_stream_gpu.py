@@ -7,8 +7,9 @@ to sixteen channel vectors; and two shapes with items of ~43 MB, the smallest si
 part of the item lies outside every CTA's ring after the first phase, so that the second phase
 fetches chunks again on its backward walk.
 
-The dispatcher only sends items of at least 32 MB there; NVN_FORCE_VARIANT=nlc=stream (read
-when the library is loaded) lifts the size rule, so the checks run in a child process.
+The dispatcher only sends large items there (or mid-size items that it can spread over CTA
+groups); NVN_FORCE_VARIANT=nlc=stream (read when the library is loaded) lifts the size rule
+and stream_groups=K fixes the number of CTA groups, so the checks run in a child process.
 """
 import os
 import subprocess
@@ -64,10 +65,43 @@ print("stream ok")
 """
 
 
-@pytest.mark.parametrize("variant", ["nlc=stream", "nlc=stream,stream_block=256"])
+@pytest.mark.parametrize("variant", ["nlc=stream", "nlc=stream,stream_block=256",
+                                     "nlc=stream,stream_groups=3", "nlc=stream,stream_groups=8"])
 def test_persistent_channels_last_kernels_on_small_and_ragged_items(tmp_path, variant):
     script = tmp_path / "stream_worker.py"
     script.write_text(_WORKER)
     env = dict(os.environ, NVN_ROOT=ROOT, NVN_FORCE_VARIANT=variant)
     r = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "stream ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_mid_size_items_run_in_cta_groups_by_default():
+    """Items of a few MB: the dispatcher picks the persistent kernels with several CTA groups
+    (each group its own items and its own barrier); parity and repeatability as above."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import _gpu_util as U
+    import atex_b200 as A
+    from atex_b200 import _lib
+    lib = _lib.load()
+    for i, (N, C, sp, dt) in enumerate([(8, 32, (64, 64, 32), "f16"),     # 8.4 MB items
+                                        (5, 64, (40, 40, 40), "bf16"),    # 8.2 MB, odd item count
+                                        (3, 16, (96, 96, 60), "f32")]):   # 35 MB items, 3 of them
+        code = {"f32": 0, "f16": 1, "bf16": 2}[dt]
+        D = 1
+        for v in sp:
+            D *= v
+        for op in (2, 3):
+            plan = _lib.describe_plan(op, code, N, C, D, 0)
+            assert plan.startswith("nlc persistent") and "groups=" in plan, plan
+        x, dy, g, b = U.rand_in(N, C, sp, False, dt, seed=300 + i)
+        U.check_in(x, dy, g, b, 1e-3, False)
+        xd, dyd, gd, bd = x.cuda(), dy.cuda(), g.cuda(), b.cuda()
+        y1, m1, s1 = A.fused_instance_norm_op(xd, gd, bd, data_format="N...C")
+        y2, m2, s2 = A.fused_instance_norm_op(xd, gd, bd, data_format="N...C")
+        d1 = A.fused_instance_norm_grad_op(dyd, xd, gd, m1, s1, data_format="N...C")
+        d2 = A.fused_instance_norm_grad_op(dyd, xd, gd, m1, s1, data_format="N...C")
+        torch.cuda.synchronize()
+        assert torch.equal(y1, y2) and torch.equal(m1, m2) and torch.equal(s1, s2)
+        assert all(torch.equal(a, b_) for a, b_ in zip(d1, d2))
+    assert lib.nvn_device_status() == 0
