@@ -51,7 +51,8 @@ namespace {
 
 constexpr int kVPC = 4;      // 128-bit vectors per consumer thread and chunk (all tensors together)
 constexpr int kStages = 6;   // ring stages of BLOCK * kVPC * 16 bytes
-constexpr int kMaxC = 128;   // bounds the per-channel arrays in shared memory
+constexpr int kMaxC = 256;   // bounds the per-channel arrays in shared memory
+constexpr int kSlotC = 128;  // channels per warp slot of the partial buffer; wider items share slots
 constexpr unsigned kGridPollLimit = 1u << 24;
 constexpr int kMaxGroups = 8;
 constexpr int kCounterStride = 32;   // unsigneds between two groups' barrier counters (128 bytes)
@@ -130,7 +131,7 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
   constexpr unsigned kTensorBytes = kStageBytes / NT;
 
   extern __shared__ __align__(128) unsigned char ring[];  // [kStages][NT][VPT][BLOCK] vectors
-  __shared__ float wpart[3][NW][kMaxC];   // per-warp partials, then per-slice partials
+  __shared__ float wpart[3][NW * kSlotC];  // per-warp partials [slot][C], then per-slice partials
   __shared__ float fin[3][kMaxC];         // per-channel coefficients of the current item
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -320,34 +321,62 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
           f0[e] = K[e] + d;
         }
       }
-      if (lane < CV) {
+      // One slot of C floats per warp; with more than kSlotC channels there are half as many
+      // slots as warps: the upper half of the warps writes first, then each warp of the lower
+      // half folds its own partial on top of its partner's.
+      const int nslots = C > kSlotC ? NW / 2 : NW;
+      auto put = [&](int slot) {
+        if (lane < CV) {
 #pragma unroll
-        for (int e = 0; e < EPV; ++e) {
-          wpart[0][warp][lane * EPV + e] = f0[e];
-          wpart[1][warp][lane * EPV + e] = f1[e];
-          wpart[2][warp][lane * EPV + e] = cnt;
+          for (int e = 0; e < EPV; ++e) {
+            wpart[0][slot * C + lane * EPV + e] = f0[e];
+            wpart[1][slot * C + lane * EPV + e] = f1[e];
+            wpart[2][slot * C + lane * EPV + e] = cnt;
+          }
         }
+      };
+      if (C > kSlotC) {
+        if (warp >= nslots) put(warp - nslots);
+        __syncthreads();
+        if (warp < nslots && lane < CV) {
+          const float on = wpart[2][warp * C + lane * EPV];
+          float nn = cnt;
+#pragma unroll
+          for (int e = 0; e < EPV; ++e) {
+            const float om = wpart[0][warp * C + lane * EPV + e];
+            const float oq = wpart[1][warp * C + lane * EPV + e];
+            if constexpr (BWD) {
+              f0[e] += om;
+              f1[e] += oq;
+            } else {
+              nn = cnt;
+              wf_merge(f0[e], f1[e], nn, om, oq, on);
+            }
+          }
+          if constexpr (!BWD) cnt = nn;
+        }
+        if (warp < nslots) put(warp);
+      } else {
+        put(warp);
       }
       __syncthreads();
       float* mine = part + ((barriers & 1) * G + b) * 3 * C;
       if (tid < C) {
-        float m = wpart[0][0][tid], s = wpart[1][0][tid], k = wpart[2][0][tid];
+        float m = wpart[0][tid], s = wpart[1][tid], k = wpart[2][tid];
         if constexpr (BWD) {
-#pragma unroll
-          for (int w = 1; w < NW; ++w) {
-            m += wpart[0][w][tid];
-            s += wpart[1][w][tid];
+          for (int w = 1; w < nslots; ++w) {
+            m += wpart[0][w * C + tid];
+            s += wpart[1][w * C + tid];
           }
         } else {
           // sums about warp 0's mean (see above), added in warp order
           const float K0 = m;
           float s1 = 0.f;
-#pragma unroll
-          for (int w = 1; w < NW; ++w) {
-            const float kw = wpart[2][w][tid], d = wpart[0][w][tid] - K0;
+          for (int w = 1; w < nslots; ++w) {
+            const float kw = wpart[2][w * C + tid], d = wpart[0][w * C + tid] - K0;
             k += kw;
             s1 = fmaf(kw, d, s1);
-            s += fmaf(kw * d, d, wpart[1][w][tid]);
+            s += fmaf(kw * d, d, wpart[1][w * C + tid]);
           }
           const float d = k > 0.f ? s1 / k : 0.f;
           m = K0 + d;
@@ -379,7 +408,7 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
 
     // ------------------------------- totals of the item: every CTA merges all partials
     {
-      const int SL = BLOCK / static_cast<int>(C);   // threads per channel (C <= 128: >= 2)
+      const int SL = BLOCK / static_cast<int>(C);   // threads per channel (C <= 256 <= BLOCK)
       const int c = tid % static_cast<int>(C), slice = tid / static_cast<int>(C);
       const float* all = part + parity * G * 3 * C;
       // Forward: the (mean, M2, n) partials are restated as sums about CTA 0's mean K of
@@ -411,9 +440,9 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
           }
         }
       }
-      float* flat0 = &wpart[0][0][0];
-      float* flat1 = &wpart[1][0][0];
-      float* flat2 = &wpart[2][0][0];
+      float* flat0 = &wpart[0][0];
+      float* flat1 = &wpart[1][0];
+      float* flat2 = &wpart[2][0];
       // (every thread passed the grid barrier after its last read of wpart)
       flat0[slice * C + c] = m;
       flat1[slice * C + c] = s;

@@ -84,7 +84,7 @@ cudaError_t nlc_onchip_launch(int dtype, bool bwd, const void* dy, const void* x
 // Persistent channels-last InstanceNorm for items far larger than shared memory
 // (nlc_stream.cu): one cooperative launch per direction, the tail of every item stays on
 // chip between the statistics and the normalisation.  nlc_stream_ok: 128-bit accesses, a
-// power-of-two number (<= 32) of channel vectors, C <= 128 (whether the items are large
+// power-of-two number (<= 32) of channel vectors, C <= 256 (whether the items are large
 // enough to be worth it is the dispatcher's decision).  `ws` holds
 // nlc_stream_workspace_bytes; the backward launch leaves colpart[N][2][C].  `block`: 512
 // threads (one CTA per SM) or 256 (two per SM).  `groups`: CTA groups that work on

@@ -449,7 +449,7 @@ constexpr int kStreamBlock = 512;  // threads per CTA of the persistent channels
 // CTA groups of the persistent kernels, or 0 when the two-phase kernels are the better
 // choice.  One group for items that keep every SM busy for tens of microseconds; smaller
 // items share the GPU, so that one group's barrier and merge hide under another group's
-// streaming: about 64 MB in flight forward, 32 MB backward (whose first phase reads twice
+// streaming: about 96 MB in flight forward, 32 MB backward (whose first phase reads twice
 // as much per item), in powers of two, at most one group per item.  Measured on B200,
 // fp16, C = 32: 8 items of 16.8 MB, two-phase 217 us, persistent with 1 / 2 / 4 / 8 groups
 // 229 / 170 / 166 / 176 us; 16 items of 7 MB, 183 us against 310 / 197 / 152 / 141 us.
@@ -459,7 +459,7 @@ int stream_groups(int dtype, bool bwd, int64_t N, int64_t C, int64_t D) {
   if (variant().stream_groups > 0) {
     g = variant().stream_groups;
   } else {
-    const double want = (bwd ? 32.0 : 64.0) * 1048576.0 / item_bytes;
+    const double want = (bwd ? 32.0 : 96.0) * 1048576.0 / item_bytes;
     while (g < 8 && want > g * 1.4142) g *= 2;   // the nearest power of two
   }
   if (g > N) g = static_cast<int>(N);

@@ -34,6 +34,8 @@ cases = [  # N, C, spatial, dtype
     (2, 64, (40, 40, 40), "bf16"),     # 8 channel vectors, 64000 voxels
     (2, 16, (99, 101), "f32"),         # fp32: 4 channel vectors of 4
     (4, 128, (50, 31), "f16"),         # 16 channel vectors, C = 128
+    (3, 256, (33, 29), "bf16"),        # 32 channel vectors, C = 256: warps share partial slots
+    (2, 128, (45, 20), "f32"),         # fp32 at its widest: 32 channel vectors of 4
     (1, 32, (7, 3), "f16"),            # 21 voxels: almost every CTA is idle
     (5, 32, (128, 128), "f32"),        # several items back to back
     (2, 32, (101, 103, 64), "f16"),    # 42.6 MB items: more chunks per CTA than ring stages
