@@ -54,7 +54,7 @@ constexpr int kStages = 6;   // ring stages of BLOCK * kVPC * 16 bytes
 constexpr int kMaxC = 256;   // bounds the per-channel arrays in shared memory
 constexpr int kSlotC = 128;  // channels per warp slot of the partial buffer; wider items share slots
 constexpr unsigned kGridPollLimit = 1u << 24;
-constexpr int kMaxGroups = 8;
+constexpr int kMaxGroups = 160;   // up to one group per CTA
 constexpr int kCounterStride = 32;   // unsigneds between two groups' barrier counters (128 bytes)
 constexpr size_t kHeaderBytes = kMaxGroups * kCounterStride * sizeof(unsigned);
 constexpr int kMergeBatch = 8;  // per-CTA partials fetched together when the item's totals are formed
@@ -581,6 +581,7 @@ static cudaError_t stream_launch_b(StreamArgs& a, cudaStream_t s) {
   e = cudaMemsetAsync(a.counter, 0, kHeaderBytes, s);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
+  if (a.groups > device_sm_count() * per_sm) a.groups = device_sm_count() * per_sm;
   const int ctas = device_sm_count() * per_sm / a.groups * a.groups;
   cfg.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
   cfg.blockDim = dim3(BLOCK, 1, 1);

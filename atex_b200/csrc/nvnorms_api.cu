@@ -450,9 +450,12 @@ constexpr int kStreamBlock = 512;  // threads per CTA of the persistent channels
 // choice.  One group for items that keep every SM busy for tens of microseconds; smaller
 // items share the GPU, so that one group's barrier and merge hide under another group's
 // streaming: about 96 MB in flight forward, 32 MB backward (whose first phase reads twice
-// as much per item), in powers of two, at most one group per item.  Measured on B200,
-// fp16, C = 32: 8 items of 16.8 MB, two-phase 217 us, persistent with 1 / 2 / 4 / 8 groups
-// 229 / 170 / 166 / 176 us; 16 items of 7 MB, 183 us against 310 / 197 / 152 / 141 us.
+// as much per item), at most one group per item.  Group counts: powers of two up to 16,
+// then a quarter, a half and all of the SMs (37, 74, 148 groups of 4, 2, 1 CTAs on B200).
+// Measured on B200, fp16, forward + backward: 8 items of 16.8 MB (C = 32), two-phase 217 us,
+// 1 / 2 / 4 / 8 groups 229 / 170 / 166 / 176 us; 16 items of 7 MB, 183 us against 310 / 197 /
+// 152 / 141 us; 32 items of 2 MB, 119 us against 110 / 88 / 83 us with 8 / 16 / 32 groups;
+// 64 items of 256 KB, 53 us against 100 / 57 / 39 / 30 us with 8 / 16 / 37 / 64 groups.
 int stream_groups(int dtype, bool bwd, int64_t N, int64_t C, int64_t D) {
   const double item_bytes = static_cast<double>(D) * C * (dtype == 0 ? 4 : 2);
   int g = 1;
@@ -460,11 +463,18 @@ int stream_groups(int dtype, bool bwd, int64_t N, int64_t C, int64_t D) {
     g = variant().stream_groups;
   } else {
     const double want = (bwd ? 32.0 : 96.0) * 1048576.0 / item_bytes;
-    while (g < 8 && want > g * 1.4142) g *= 2;   // the nearest power of two
+    const int sm = device_sm_count();
+    const int cand[] = {1, 2, 4, 8, 16, sm / 4, sm / 2, sm};
+    for (int c : cand)   // the candidate nearest to `want` on a log scale (ascending list)
+      if (c > g && static_cast<double>(c) * g < want * want) g = c;
   }
   if (g > N) g = static_cast<int>(N);
   if (variant().nlc == 3) return g;
-  return (item_bytes >= 32.0 * 1048576.0 || g * item_bytes >= 24.0 * 1048576.0) ? g : 0;
+  const double in_flight = g * item_bytes;
+  return (item_bytes >= 32.0 * 1048576.0 || in_flight >= 24.0 * 1048576.0 ||
+          (g >= 16 && in_flight >= 8.0 * 1048576.0))
+             ? g
+             : 0;
 }
 
 struct NlcPlan {
@@ -484,7 +494,9 @@ int plan_nlc(int dtype, bool bwd, int64_t N, int64_t C, int64_t D, bool vec_ok, 
   p->scalar = !(vec_ok && C % V == 0);
   // Small items: a warp per item beats a CTA per item below 2048 elements, and is the only
   // one-launch path for channel counts or alignments the vector kernels cannot take.
+  // (items that fit in one CTA's shared memory keep their single-pass kernel)
   if (vec_ok && allow_onchip && variant().nlc != 1 && nlc_stream_ok(dtype, N, C, D) &&
+      (variant().nlc == 3 || !nlc_onchip_ok(dtype, bwd, C, D)) &&
       stream_groups(dtype, bwd, N, C, D) > 0) {
     p->stream = true;
     size_t off = nlc_stream_workspace_bytes(bwd, N, C);
