@@ -179,6 +179,20 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
   };
   const int64_t first_v0 = static_cast<int64_t>(b) * kChunkVecs;             // chunk 0
   const int last_stage = NCi > 0 ? (NCi - 1) % kStages : 0;                  // of chunk NC - 1
+  // Only the item's last chunk can be short, and it is the last chunk of the CTA that has
+  // it.  Every other chunk takes a path without a single per-vector test or address
+  // computation: this thread's view of a stage is one pointer (its slot of vector 0; the
+  // other slots, tensors and the global vectors lie at compile-time offsets from it).
+  const bool tail_short = NCi > 0 && first_v0 + (NC - 1) * stride + kChunkVecs > item_vecs;
+  const int n_whole = NCi - (tail_short ? 1 : 0);
+  unsigned char* const my_ring = ring + tid * 16;
+  auto issue_whole = [&](const P* const (&from)[NT], unsigned char* tp) {
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int u = 0; u < VPT; ++u)
+        cp_async16(tp + t * kTensorBytes + u * (BLOCK * 16), from[t] + u * BLOCK);
+  };
 
   // Copy groups: one per step, committed right after the step's data has been consumed,
   // for the chunk that will occupy the same stage kStages steps later; a step first waits
@@ -207,14 +221,16 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
     // phase 2, in an order that the group count does not cover: wait for all of them once
     if (barriers > 0) cp_async_wait<0>();
     {
-    int stage = 0;
-    int64_t v0 = first_v0;
-    for (int c = 0; c < NCi; ++c) {
-      cp_async_wait<kStages - 1>();
-      const int nv = v0 + kChunkVecs <= item_vecs ? VPT : count_at(v0);
-      const P* px = reinterpret_cast<const P*>(ring + stage * kStageBytes) + tid;
-      if constexpr (!BWD) {
-        if (nv == VPT) {
+      // this thread's vector 0 of the chunk being read, and of the chunk kStages further on
+      const P* ahead[NT];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) ahead[t] = src[t] + n * item_vecs + first_v0 + kStages * stride + tid;
+      unsigned char* tp = my_ring;
+      int c = 0;
+      for (; c < n_whole; ++c) {
+        cp_async_wait<kStages - 1>();
+        const P* px = reinterpret_cast<const P*>(tp);
+        if constexpr (!BWD) {
           // exact batch (mean, centred squares) folded into the running triple (Chan)
           E v[VPT][NE];
 #pragma unroll
@@ -241,24 +257,9 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
           }
           cnt = nn;
         } else {
-          for (int u = 0; u < nv; ++u) {
-            E v[NE];
-            unpack<T, EPV>(px[u * BLOCK], v);
-            cnt += 1.f;
-            const E inv = M::bcast(1.0f / cnt);
+          const P* pd = reinterpret_cast<const P*>(tp + kTensorBytes);
 #pragma unroll
-            for (int e = 0; e < NE; ++e) {
-              const E dl = M::fma(acc0[e], M::bcast(-1.f), v[e]);
-              acc0[e] = M::fma(dl, inv, acc0[e]);
-              acc1[e] = M::fma(dl, M::fma(acc0[e], M::bcast(-1.f), v[e]), acc1[e]);
-            }
-          }
-        }
-      } else {
-        const P* pd = reinterpret_cast<const P*>(ring + stage * kStageBytes + kTensorBytes) + tid;
-#pragma unroll
-        for (int u = 0; u < VPT; ++u) {
-          if (u < nv) {
+          for (int u = 0; u < VPT; ++u) {
             E vx[NE], vd[NE];
             unpack<T, EPV>(px[u * BLOCK], vx);
             unpack<T, EPV>(pd[u * BLOCK], vd);
@@ -269,13 +270,45 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
             }
           }
         }
+        // the last kStages chunks stay where they are for phase 2
+        if (c + kStages < n_whole) {
+          issue_whole(ahead, tp);
+        } else if (c + kStages < NCi) {
+          issue(n, first_v0 + (c + kStages) * stride, c % kStages);   // the short tail
+        }
+        cp_async_commit();
+#pragma unroll
+        for (int t = 0; t < NT; ++t) ahead[t] += stride;
+        tp = tp + kStageBytes == my_ring + kStages * kStageBytes ? my_ring : tp + kStageBytes;
       }
-      // the last kStages chunks stay where they are for phase 2
-      if (c + kStages < NCi) issue(n, v0 + kStages * stride, stage);
-      cp_async_commit();
-      v0 += stride;
-      stage = stage + 1 == kStages ? 0 : stage + 1;
-    }
+      if (tail_short) {   // vector by vector, with per-element Welford updates
+        cp_async_wait<kStages - 1>();
+        const int nv = count_at(first_v0 + (NC - 1) * stride);
+        const P* px = reinterpret_cast<const P*>(tp);
+        for (int u = 0; u < nv; ++u) {
+          E v[NE];
+          unpack<T, EPV>(px[u * BLOCK], v);
+          if constexpr (!BWD) {
+            cnt += 1.f;
+            const E inv = M::bcast(1.0f / cnt);
+#pragma unroll
+            for (int e = 0; e < NE; ++e) {
+              const E dl = M::fma(acc0[e], M::bcast(-1.f), v[e]);
+              acc0[e] = M::fma(dl, inv, acc0[e]);
+              acc1[e] = M::fma(dl, M::fma(acc0[e], M::bcast(-1.f), v[e]), acc1[e]);
+            }
+          } else {
+            E vd[NE];
+            unpack<T, EPV>(reinterpret_cast<const P*>(tp + kTensorBytes)[u * BLOCK], vd);
+#pragma unroll
+            for (int e = 0; e < NE; ++e) {
+              acc0[e] = M::add(acc0[e], vd[e]);
+              acc1[e] = M::fma(vd[e], M::add(v[e], nmu[e]), acc1[e]);
+            }
+          }
+        }
+        cp_async_commit();
+      }
     }
 
     // ------------------------------------------- CTA partial of every channel
@@ -492,47 +525,58 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
     lanes_from<EPV>(&fin[0][cv * EPV], k0);
     lanes_from<EPV>(&fin[1][cv * EPV], k1);
     lanes_from<EPV>(&fin[2][cv * EPV], k2);
-    int stage = last_stage;
-    int64_t v0 = first_v0 + (NC - 1) * stride;
-    for (int r = 0; r < NCi; ++r) {
-      // the first kStages steps find their chunk where phase 1 left it; later steps reuse
-      // the stage freed kStages steps earlier: the stage counter simply keeps counting down
-      cp_async_wait<kStages - 1>();
-      const int nv = v0 + kChunkVecs <= item_vecs ? VPT : count_at(v0);
-      const P* px = reinterpret_cast<const P*>(ring + stage * kStageBytes) + tid;
-      P* po = static_cast<P*>(a.out) + n * item_vecs + v0 + tid;
+    {
+      // normalises vector u of the stage at tp into po[u * BLOCK]
+      auto emit = [&](const unsigned char* tp, P* po, int u) {
+        E vx[NE], o[NE];
+        unpack<T, EPV>(reinterpret_cast<const P*>(tp)[u * BLOCK], vx);
+        if constexpr (!BWD) {
 #pragma unroll
-      for (int u = 0; u < VPT; ++u) {
-        if (u < nv) {
-          E vx[NE], o[NE];
-          unpack<T, EPV>(px[u * BLOCK], vx);
-          if constexpr (!BWD) {
+          for (int e = 0; e < NE; ++e) o[e] = M::fma(M::add(vx[e], k0[e]), k1[e], k2[e]);
+        } else {
+          E vd[NE];
+          unpack<T, EPV>(reinterpret_cast<const P*>(tp + kTensorBytes)[u * BLOCK], vd);
+          // dx = gamma * ivar * (dy - mean(dy) - (x - mean) * ivar * mean(dy * xhat))
 #pragma unroll
-            for (int e = 0; e < NE; ++e) o[e] = M::fma(M::add(vx[e], k0[e]), k1[e], k2[e]);
-          } else {
-            const P* pd =
-                reinterpret_cast<const P*>(ring + stage * kStageBytes + kTensorBytes) + tid;
-            E vd[NE];
-            unpack<T, EPV>(pd[u * BLOCK], vd);
-            // dx = gamma * ivar * (dy - mean(dy) - (x - mean) * ivar * mean(dy * xhat))
-#pragma unroll
-            for (int e = 0; e < NE; ++e) {
-              const E t = M::fma(M::add(vx[e], nmu[e]), k2[e], k1[e]);
-              o[e] = M::mul(k0[e], M::fma(t, M::bcast(-1.f), vd[e]));
-            }
+          for (int e = 0; e < NE; ++e) {
+            const E t = M::fma(M::add(vx[e], nmu[e]), k2[e], k1[e]);
+            o[e] = M::mul(k0[e], M::fma(t, M::bcast(-1.f), vd[e]));
           }
-          store_stream<T, EPV>(reinterpret_cast<T*>(po + u * BLOCK), 0, repack<T, EPV>(o));
         }
+        store_stream<T, EPV>(reinterpret_cast<T*>(po + u * BLOCK), 0, repack<T, EPV>(o));
+      };
+      // The first kStages steps find their chunk where phase 1 left it; later steps reuse
+      // the stage freed kStages steps earlier: the stage simply keeps counting down.  The
+      // freed slots take the chunk kStages steps further down the backward walk or, once
+      // there is none, this CTA's chunk `stage` of the group's next item.
+      int stage = last_stage;
+      unsigned char* tp = my_ring + last_stage * kStageBytes;
+      const int64_t top = n * item_vecs + first_v0 + (NC - 1) * stride + tid;   // vector 0 of the last chunk
+      P* po = static_cast<P*>(a.out) + top;
+      const P* behind[NT];   // this thread's vector 0 of the chunk kStages steps further down
+#pragma unroll
+      for (int t = 0; t < NT; ++t) behind[t] = src[t] + top - kStages * stride;
+      for (int r = 0; r < NCi; ++r) {
+        cp_async_wait<kStages - 1>();
+        if (r == 0 && tail_short) {
+          const int nv = count_at(first_v0 + (NC - 1) * stride);
+          for (int u = 0; u < nv; ++u) emit(tp, po, u);
+        } else {
+#pragma unroll
+          for (int u = 0; u < VPT; ++u) emit(tp, po, u);
+        }
+        if (r + kStages < NCi) {
+          issue_whole(behind, tp);
+        } else if (n + groups < N && stage < NCi) {
+          issue(n + groups, first_v0 + stage * stride, stage);
+        }
+        cp_async_commit();
+        po -= stride;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) behind[t] -= stride;
+        tp = stage == 0 ? tp + (kStages - 1) * kStageBytes : tp - kStageBytes;
+        stage = stage == 0 ? kStages - 1 : stage - 1;
       }
-      // the slots are free: the next chunk of the backward walk, or the next item's phase 1
-      if (r + kStages < NCi) {
-        issue(n, v0 - kStages * stride, stage);
-      } else if (n + groups < N && stage < NCi) {
-        issue(n + groups, first_v0 + stage * stride, stage);
-      }
-      cp_async_commit();
-      v0 -= stride;
-      stage = stage == 0 ? kStages - 1 : stage - 1;
     }
     // the coefficients in `fin` and the partials in `wpart` are rewritten by the next item
     __syncthreads();
