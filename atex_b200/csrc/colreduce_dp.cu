@@ -80,6 +80,15 @@ __device__ __forceinline__ void st_pair(uint2* p, float v, unsigned epoch) {
                "r"(epoch)
                : "memory");
 }
+// two neighbouring pairs with one 16-byte load: {value, epoch, value, epoch}
+__device__ __forceinline__ uint4 ld_two_pairs(const uint2* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
 __device__ __forceinline__ uint2 ld_pair(const uint2* p) {
   uint2 v;
   asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
@@ -138,23 +147,42 @@ __global__ void __launch_bounds__(kTX* TY)
     if (tx == 0 && ty == 0) publish_epoch(c, kWord, epoch);
     return;
   }
-  // bounded poll of this rank's own receive rows, then the sum in rank order
+  // Bounded poll of this rank's own receive rows, then the sum in rank order.  The pairs of
+  // four ranks are fetched together (eight independent 16-byte loads): in the steady state
+  // everything has arrived, and reading world * kW pairs one after the other would cost as
+  // many L2 round trips (20 us at eight ranks).  Only pairs whose epoch is still old are
+  // read again.
   int ok = 1;
   unsigned polls = 0;
   float acc[kW] = {0.f, 0.f, 0.f, 0.f};
+  static_assert(kW == 4, "two 16-byte loads per rank and thread");
   if (ty == 0 && col < F2) {
-    for (int r = 0; r < c.world; ++r) {
-      const uint2* src = c.recv[c.rank] + (slot + r) * F2 + col;
+    const uint2* base = c.recv[c.rank] + slot * F2 + col;
+    for (int r0 = 0; r0 < c.world; r0 += 4) {
+      uint4 got[4][2];
 #pragma unroll
-      for (int w = 0; w < kW; ++w) {
-        uint2 v = ld_pair(src + w);
-        // one budget for the whole thread: after the first element that never arrives the
-        // rest are read once and not waited for, so a missing peer costs one time-out
-        while (v.y != epoch && ok) {
-          if (++polls > kPollLimit) ok = 0;
-          v = ld_pair(src + w);
+      for (int i = 0; i < 4; ++i) {
+        if (r0 + i < c.world) {
+          got[i][0] = ld_two_pairs(base + (r0 + i) * F2);
+          got[i][1] = ld_two_pairs(base + (r0 + i) * F2 + 2);
         }
-        acc[w] += __uint_as_float(v.x);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (r0 + i < c.world) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint4 v = got[i][h];
+            // one budget for the whole thread: after the first element that never arrives the
+            // rest are read once and not waited for, so a missing peer costs one time-out
+            while ((v.y != epoch || v.w != epoch) && ok) {
+              if (++polls > kPollLimit) ok = 0;
+              v = ld_two_pairs(base + (r0 + i) * F2 + 2 * h);
+            }
+            acc[2 * h] += __uint_as_float(v.x);
+            acc[2 * h + 1] += __uint_as_float(v.z);
+          }
+        }
       }
     }
 #pragma unroll
