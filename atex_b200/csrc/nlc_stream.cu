@@ -73,6 +73,7 @@ struct StreamArgs {
   float* colpart;   // backward: [N][2][C] per-item (dgamma, dbeta) contributions
   unsigned* counter;  // one barrier counter per group, kCounterStride apart, zero at launch
   int groups;         // CTA groups; gridDim.x is a multiple
+  int64_t row_channels;  // row mode (ROWS): channels of the "NC..." tensor whose rows are the items
   int64_t N, C, D;
   float eps;
   int* status;
@@ -116,7 +117,11 @@ __device__ __forceinline__ void wf_merge(float& mean, float& m2, float& n, float
   n = t;
 }
 
-template <typename T, bool BWD, int BLOCK>
+// ROWS: the items are contiguous rows of a channel-first tensor ("NC...": item n is row
+// (n / row_channels, n % row_channels), one scale and one offset per row).  A row is read as
+// D voxels of one channel vector (C = EPV), so everything up to the per-channel totals is
+// the channels-last code; one thread then merges the EPV "channels" into the row's totals.
+template <typename T, bool BWD, int BLOCK, bool ROWS>
 __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
     nlc_stream_kernel(const StreamArgs a) {
   constexpr int EPV = VecTraits<T>::kFull;
@@ -149,7 +154,7 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
   constexpr int64_t kChunkVecs = static_cast<int64_t>(VPT) * BLOCK;
   const int64_t item_chunks = (item_vecs + kChunkVecs - 1) / kChunkVecs;
   const int64_t NC = b < item_chunks ? (item_chunks - b + G - 1) / G : 0;   // chunks of this CTA
-  const float inv_D = 1.0f / static_cast<float>(D);
+  const float inv_D = 1.0f / static_cast<float>(ROWS ? D * EPV : D);
 
   // Index arithmetic is kept out of the streaming loops (a chunk is only VPT vectors per
   // thread): chunk offsets advance by a fixed stride, ring stages by a wrapping counter.
@@ -213,7 +218,7 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
     if constexpr (BWD) {
       float t[EPV];
 #pragma unroll
-      for (int e = 0; e < EPV; ++e) t[e] = -__ldg(a.mean_in + n * C + cv * EPV + e);
+      for (int e = 0; e < EPV; ++e) t[e] = -__ldg(a.mean_in + (ROWS ? n : n * C + cv * EPV + e));
 #pragma unroll
       for (int e = 0; e < NE; ++e) nmu[e] = make_float2(t[2 * e], t[2 * e + 1]);
     }
@@ -495,7 +500,12 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
           s = fmaf(-m, d, s);             // M2 about the mean
           m = K0 + d;
         }
-        if constexpr (!BWD) {
+        if constexpr (ROWS) {
+          // per-"channel" totals, merged below
+          fin[0][tid] = m;
+          fin[1][tid] = s;
+          fin[2][tid] = k;
+        } else if constexpr (!BWD) {
           const float iv = 1.0f / sqrtf(s / k + a.eps);
           fin[0][tid] = -m;                               // -mean
           fin[1][tid] = iv * __ldg(a.gamma + tid);        // scale
@@ -518,6 +528,54 @@ __global__ void __launch_bounds__(BLOCK, BLOCK <= 256 ? 2 : 1)
         }
       }
       __syncthreads();
+      if constexpr (ROWS) {
+        float c0 = 0.f, c1 = 0.f, c2 = 0.f;   // the row's three coefficients
+        if (tid == 0) {
+          const int64_t ch = n % a.row_channels, nb = n / a.row_channels;
+          if constexpr (!BWD) {
+            // (mean, M2, n) of the EPV lanes as sums about lane 0's mean, added in lane order
+            const float K = fin[0][0];
+            float s1 = 0.f, s2 = fin[1][0], kk = fin[2][0];
+            for (int e = 1; e < EPV; ++e) {
+              const float d = fin[0][e] - K, ke = fin[2][e];
+              kk += ke;
+              s1 = fmaf(ke, d, s1);
+              s2 += fmaf(ke * d, d, fin[1][e]);
+            }
+            const float d = s1 / kk;
+            const float mean = K + d, m2 = fmaf(-s1, d, s2);
+            const float iv = 1.0f / sqrtf(m2 / kk + a.eps);
+            c0 = -mean;
+            c1 = iv * __ldg(a.gamma + ch);
+            c2 = __ldg(a.beta + ch);
+            if (b == 0) {
+              a.mean[n] = mean;
+              a.ivar[n] = iv;
+            }
+          } else {
+            float sdy = fin[0][0], sdx = fin[1][0];
+            for (int e = 1; e < EPV; ++e) {
+              sdy += fin[0][e];
+              sdx += fin[1][e];
+            }
+            const float iv = __ldg(a.ivar_in + n);
+            const float dgam = sdx * iv;
+            c0 = __ldg(a.gamma + ch) * iv;
+            c1 = sdy * inv_D;
+            c2 = dgam * inv_D * iv;
+            if (b == 0) {
+              a.colpart[(nb * 2 + 0) * a.row_channels + ch] = dgam;
+              a.colpart[(nb * 2 + 1) * a.row_channels + ch] = sdy;
+            }
+          }
+          for (int e = 0; e < EPV; ++e) {
+            fin[0][e] = c0;
+            fin[1][e] = c1;
+            fin[2][e] = c2;
+          }
+        }
+        __syncthreads();
+      }
     }
 
     // ------------------------------------------------------------------ phase 2
@@ -603,9 +661,9 @@ size_t nlc_stream_workspace_bytes(bool bwd, int64_t N, int64_t C) {
   return b;
 }
 
-template <typename T, bool BWD, int BLOCK>
+template <typename T, bool BWD, int BLOCK, bool ROWS>
 static cudaError_t stream_launch_b(StreamArgs& a, cudaStream_t s) {
-  auto kernel = nlc_stream_kernel<T, BWD, BLOCK>;
+  auto kernel = nlc_stream_kernel<T, BWD, BLOCK, ROWS>;
   const size_t smem = static_cast<size_t>(kStages) * BLOCK * kVPC * 16;
   static std::atomic<uint64_t> prepared{0};
   static std::atomic<int> cached_per_sm{0};  // per process: every device is the same part
@@ -646,15 +704,19 @@ static cudaError_t stream_launch_b(StreamArgs& a, cudaStream_t s) {
 // SM, 16 KB stages)
 template <typename T, bool BWD>
 static cudaError_t stream_launch_t(StreamArgs& a, int block, cudaStream_t s) {
-  return block == 256 ? stream_launch_b<T, BWD, 256>(a, s) : stream_launch_b<T, BWD, 512>(a, s);
+  if (a.row_channels > 0) return stream_launch_b<T, BWD, 512, true>(a, s);
+  return block == 256 ? stream_launch_b<T, BWD, 256, false>(a, s)
+                      : stream_launch_b<T, BWD, 512, false>(a, s);
 }
 
 cudaError_t nlc_stream_launch(int dtype, bool bwd, const void* dy, const void* x,
                               const float* gamma, const float* beta, const float* mean_in,
                               const float* ivar_in, int64_t N, int64_t C, int64_t D, float eps,
                               void* out, float* mean, float* ivar, void* ws, float* colpart,
-                              int* status, int block, int groups, cudaStream_t s) {
+                              int* status, int block, int groups, int64_t row_channels,
+                              cudaStream_t s) {
   StreamArgs a = {};
+  a.row_channels = row_channels;
   a.groups = groups < 1 ? 1 : (groups > kMaxGroups ? kMaxGroups : groups);
   if (a.groups > N) a.groups = static_cast<int>(N > 0 ? N : 1);
   a.x = x;

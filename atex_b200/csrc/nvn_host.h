@@ -88,14 +88,19 @@ cudaError_t nlc_onchip_launch(int dtype, bool bwd, const void* dy, const void* x
 // enough to be worth it is the dispatcher's decision).  `ws` holds
 // nlc_stream_workspace_bytes; the backward launch leaves colpart[N][2][C].  `block`: 512
 // threads (one CTA per SM) or 256 (two per SM).  `groups`: CTA groups that work on
-// different items at the same time (1 to 8, clamped to N).
+// different items at the same time (clamped to N and to the grid).  `row_channels` > 0: row
+// mode for channel-first tensors - the N items are contiguous rows of D * C elements (pass
+// C = the vector width and D = row length / C), item n being row (n / row_channels,
+// n % row_channels) with gamma[n % row_channels]; mean / ivar are [N], colpart is
+// [N / row_channels][2][row_channels].
 bool nlc_stream_ok(int dtype, int64_t N, int64_t C, int64_t D);
 size_t nlc_stream_workspace_bytes(bool bwd, int64_t N, int64_t C);
 cudaError_t nlc_stream_launch(int dtype, bool bwd, const void* dy, const void* x,
                               const float* gamma, const float* beta, const float* mean_in,
                               const float* ivar_in, int64_t N, int64_t C, int64_t D, float eps,
                               void* out, float* mean, float* ivar, void* ws, float* colpart,
-                              int* status, int block, int groups, cudaStream_t s);
+                              int* status, int block, int groups, int64_t row_channels,
+                              cudaStream_t s);
 
 // Warp-per-item channels-last InstanceNorm for small items (nlc_small.cu): any dtype, C and
 // alignment, C <= 32 and D * C <= 4096 elements.  Backward leaves colpart[N][2][C].

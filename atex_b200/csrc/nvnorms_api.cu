@@ -180,8 +180,13 @@ int fail_cuda(cudaError_t e) {
 // ---------------------------------------------------------------------------
 // Plan for a contiguous-row problem ([rows, D], LayerNorm or "NC..." InstanceNorm)
 // ---------------------------------------------------------------------------
+constexpr int kStreamBlock = 512;  // threads per CTA of the persistent kernels (nlc_stream.cu)
+int stream_groups(int dtype, bool bwd, int64_t N, int64_t C, int64_t D);
+
 struct RowProblemPlan {
   bool two_phase;
+  bool stream_rows;   // channel-first rows too wide for the row-cached kernels: persistent kernels in row mode
+  int stream_groups;
   bool wide;       // LayerNorm rows that fill a shape of the split-barrier cluster kernels
   WidePlan wp;
   size_t off_colscratch;  // slab scratch of the column reduction (0 bytes: none)
@@ -269,6 +274,18 @@ int plan_rows_uncached(int dtype, bool bwd, bool row_affine, int64_t rows, int64
       p->colpart_rows = row_affine ? N : p->rows.partial_rows;
       p->off_colpart = off;
       off += align_up(static_cast<size_t>(p->colpart_rows) * 2 * (row_affine ? C : D) * 4, 256);
+    }
+  } else if (row_affine && full && var.nlc != 1 && rows <= 0x7fffffffLL &&
+             stream_groups(dtype, bwd, rows, V, D / V) > 0) {
+    // InstanceNorm "NC..." rows of hundreds of KB and more: the persistent kernels in row
+    // mode (a row is read as D / V voxels of one channel vector), in CTA groups
+    p->stream_rows = true;
+    p->stream_groups = stream_groups(dtype, bwd, rows, V, D / V);
+    off = nlc_stream_workspace_bytes(bwd, rows, V);
+    if (bwd) {
+      p->colpart_rows = N;
+      p->off_colpart = off;
+      off += align_up(static_cast<size_t>(N) * 2 * C * 4, 256);
     }
   } else {
     if (rows > 0x7fffffffLL) return NVN_ERR_UNSUPPORTED;
@@ -406,6 +423,13 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
       e = rows_fn(dtype, bwd)(row_affine, p.epv, p.shape, a, stream, false, &rp);
     }
     if (e != cudaSuccess) return fail_cuda(e);
+  } else if (p.stream_rows) {
+    const int V = full_epv(dtype);
+    cudaError_t e = nlc_stream_launch(
+        dtype, bwd, dy, x, gamma, beta, mean_in, ivar_in, rows, V, D / V, eps, out, mean, ivar, wsb,
+        bwd ? reinterpret_cast<float*>(wsb + p.off_colpart) : nullptr, device_status_word(),
+        kStreamBlock, p.stream_groups, C, stream);
+    if (e != cudaSuccess) return fail_cuda(e);
   } else {
     R2Args a = {};
     a.x = x;
@@ -444,7 +468,6 @@ int run_rows(int dtype, bool bwd, bool row_affine, const void* dy, const void* x
 // ---------------------------------------------------------------------------
 // Plan for channels-last InstanceNorm (x[n, d, c])
 // ---------------------------------------------------------------------------
-constexpr int kStreamBlock = 512;  // threads per CTA of the persistent channels-last kernels
 
 // CTA groups of the persistent kernels, or 0 when the two-phase kernels are the better
 // choice.  One group for items that keep every SM busy for tens of microseconds; smaller
@@ -580,7 +603,7 @@ int run_nlc(int dtype, bool bwd, const void* dy, const void* x, const float* gam
     cudaError_t e = nlc_stream_launch(dtype, bwd, dy, x, gamma, beta, mean_in, ivar_in, N, C, D,
                                       eps, out, mean, ivar, wsb, colpart, device_status_word(),
                                       variant().stream_block > 0 ? variant().stream_block : kStreamBlock,
-                                      stream_groups(dtype, bwd, N, C, D), stream);
+                                      stream_groups(dtype, bwd, N, C, D), 0, stream);
     if (e != cudaSuccess) return fail_cuda(e);
     if (bwd) {
       e = comm != nullptr ? colreduce_allreduce_launch(colpart, N, C, comm, dgamma, dbeta, stream)
@@ -1056,6 +1079,9 @@ int nvn_describe_plan(int op, int dtype, int64_t N, int64_t C, int64_t D, int ch
   if (p.wide) {
     snprintf(out, out_bytes, "rows wide block=%d vpt=%d cluster=%d stages=%d epv=%d grid=%d",
              p.wp.block, p.wp.vpt, p.wp.cluster, p.wp.stages, full_epv(dtype), p.wp.grid);
+  } else if (p.stream_rows) {
+    snprintf(out, out_bytes, "rows persistent epv=%d consumers=%d ring=6x32KB groups=%d",
+             full_epv(dtype), kStreamBlock, p.stream_groups);
   } else if (p.two_phase) {
     snprintf(out, out_bytes, "rows two-phase epv=%d chunk=%lld nchunks=%d slices=%d",
              p.scalar ? 1 : full_epv(dtype), static_cast<long long>(p.r2.chunk), p.r2.nchunks,

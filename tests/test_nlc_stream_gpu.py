@@ -107,3 +107,50 @@ def test_mid_size_items_run_in_cta_groups_by_default():
         assert torch.equal(y1, y2) and torch.equal(m1, m2) and torch.equal(s1, s2)
         assert all(torch.equal(a, b_) for a, b_ in zip(d1, d2))
     assert lib.nvn_device_status() == 0
+
+
+_ROW_WORKER = r"""
+import os, sys
+sys.path.insert(0, os.environ["NVN_ROOT"]); sys.path.insert(0, os.path.join(os.environ["NVN_ROOT"], "tests"))
+import torch
+from atex_b200 import _lib
+import atex_b200 as A
+import _gpu_util as U
+lib = _lib.load()
+cases = [  # N, C, spatial, dtype: channel-first rows wider than the row-cached kernels take
+    (2, 4, (100, 101, 64), "f16"),     # 8 rows of 1.29 MB, not a whole number of chunks
+    (3, 8, (128, 128, 40), "bf16"),    # 24 rows of 1.31 MB
+    (2, 16, (70, 60, 64), "f32"),      # 32 rows of 1.07 MB, fp32
+    (1, 3, (90, 90, 90), "f16"),       # 3 rows: fewer rows than CTA groups wanted
+]
+for i, (N, C, sp, dt) in enumerate(cases):
+    code = {"f32": 0, "f16": 1, "bf16": 2}[dt]
+    D = 1
+    for s in sp: D *= s
+    for op in (2, 3):
+        plan = _lib.describe_plan(op, code, N, C, D, 1)
+        assert plan.startswith("rows persistent"), plan
+    x, dy, g, b = U.rand_in(N, C, sp, True, dt, seed=400 + i)
+    U.check_in(x, dy, g, b, 1e-3, True)
+    xd, dyd, gd, bd = x.cuda(), dy.cuda(), g.cuda(), b.cuda()
+    y1, m1, s1 = A.fused_instance_norm_op(xd, gd, bd, data_format="NC...")
+    y2, m2, s2 = A.fused_instance_norm_op(xd, gd, bd, data_format="NC...")
+    d1 = A.fused_instance_norm_grad_op(dyd, xd, gd, m1, s1, data_format="NC...")
+    d2 = A.fused_instance_norm_grad_op(dyd, xd, gd, m1, s1, data_format="NC...")
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y2) and torch.equal(m1, m2) and torch.equal(s1, s2)
+    assert all(torch.equal(p, q) for p, q in zip(d1, d2))
+assert lib.nvn_device_status() == 0
+print("rows ok")
+"""
+
+
+@pytest.mark.parametrize("variant", ["nlc=stream", "nlc=stream,stream_groups=5"])
+def test_persistent_kernels_in_row_mode_on_channel_first_rows(tmp_path, variant):
+    """InstanceNorm "NC..." rows of a MB and more run the persistent kernels in row mode (a
+    row is an item of one channel vector per voxel); forced for every batch size here."""
+    script = tmp_path / "row_worker.py"
+    script.write_text(_ROW_WORKER)
+    env = dict(os.environ, NVN_ROOT=ROOT, NVN_FORCE_VARIANT=variant)
+    r = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "rows ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
