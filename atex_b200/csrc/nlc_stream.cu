@@ -30,7 +30,10 @@
 //     moves nothing) would cost more than the streaming: the grid then splits into GROUPS
 //     of CTAs (CTA i belongs to group i % groups), each with its own barrier and its own
 //     items (n = group, group + groups, ...), so that one group streams while another
-//     one waits; such items stay in shared memory as a whole or nearly so.
+//     one waits; such items stay in shared memory as a whole or nearly so;
+//   * ROW MODE serves channel-first ("NC...") tensors whose rows are too long for the
+//     row-cached kernels: a row is an item of one channel vector per voxel, and the lanes
+//     of the vector are merged into the row's totals at the end (see the ROWS flag).
 //
 // All merges have a fixed order (lanes by butterfly, warps and CTAs by index), so results
 // are bit-identical run to run.  No multicast copy; every copy reads this GPU's memory.
@@ -40,7 +43,10 @@
 // (atex/nv_norms/cc/kernels/fused_instance_norm_op.cu:52-69, 80-101, 809-818) and
 // InstanceNormRowReduceInToTempFused / TempToOutFused / UpdateFusedVectorized
 // (fused_instance_norm_op.cu:666-730, 103-146, 744-763), and the host functions that
-// launch them (:1314-1407).
+// launch them (:1314-1407); in row mode, for rows beyond the shared-memory kernels, the
+// channel-first chain GeneralNormRowReduceInToOutWelford + InstanceNormUpdate
+// (fused_instance_norm_op.cu:1167-1194, 809-818), InstanceNormToTempWelford (NC... branch,
+// :23-70) and InstanceNormRowReduceInToOutFused / UpdateFusedVectorized (:315-366, 744-763).
 #include <atomic>
 
 #include "nvn_common.cuh"
