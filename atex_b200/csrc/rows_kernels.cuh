@@ -249,7 +249,8 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
   // as CTAs of this one retire, and this one may have been scheduled while its predecessor
   // was still running - nothing that the predecessor may have written (activations,
   // parameters) is read before griddep_wait().
-  griddep_launch_dependents();
+  // (cluster kernels neither launch early nor let their successor: see the launcher)
+  if constexpr (CS == 1) griddep_launch_dependents();
   griddep_wait();
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(8) uint64_t ring_bars[STAGES];
@@ -470,7 +471,8 @@ __global__ void __launch_bounds__(RowBlock<TPR, MINB>::kBlock)
 
   // The column reduction that follows may be scheduled as CTAs of this kernel retire; this
   // kernel itself reads nothing its predecessor may have written before griddep_wait().
-  griddep_launch_dependents();
+  // (cluster kernels neither launch early nor let their successor: see the launcher)
+  if constexpr (CS == 1) griddep_launch_dependents();
   griddep_wait();
   extern __shared__ __align__(128) unsigned char ring_mem[];
   __shared__ __align__(8) uint64_t ring_bars[STAGES];
@@ -939,11 +941,12 @@ inline cudaError_t launch_rows_exact(const RowsArgs& a, cudaStream_t stream, boo
   // (LayerNorm [4096, 4096] bf16: 36.6 -> 35.4 us per step), but CTAs of the next kernel that
   // become resident early and wait take room from a long kernel's successors - InstanceNorm
   // bf16 NC... [64, 256, 128, 128] ran 3 % slower with it, fp16 [64, 256, 32, 32, 32] with
-  // its cluster backward 44 % slower.
+  // its cluster backward 44 % slower.  Cluster kernels of any size stay out of it: [2, 256,
+  // 32, 32, 32] (33 MB) took 49 us per step with dependent launches and 39 us without.
   const bool short_kernel =
       static_cast<int64_t>(a.N) * a.D * static_cast<int64_t>(sizeof(T)) < (int64_t(64) << 20);
   attr[0].val.programmaticStreamSerializationAllowed =
-      use_dependent_launch() && short_kernel ? 1 : 0;
+      use_dependent_launch() && short_kernel && CS == 1 ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (CS > 1) {
