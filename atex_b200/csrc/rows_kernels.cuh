@@ -944,7 +944,7 @@ inline cudaError_t launch_rows_exact(const RowsArgs& a, cudaStream_t stream, boo
   // its cluster backward 44 % slower.  Cluster kernels of any size stay out of it: [2, 256,
   // 32, 32, 32] (33 MB) took 49 us per step with dependent launches and 39 us without.
   const bool short_kernel =
-      static_cast<int64_t>(a.N) * a.D * static_cast<int64_t>(sizeof(T)) < (int64_t(64) << 20);
+      static_cast<int64_t>(a.N) * a.D * static_cast<int64_t>(sizeof(T)) <= (int64_t(128) << 20);
   attr[0].val.programmaticStreamSerializationAllowed =
       use_dependent_launch() && short_kernel && CS == 1 ? 1 : 0;
   cfg.attrs = attr;
